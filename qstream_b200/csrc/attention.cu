@@ -1,0 +1,245 @@
+// Rotary position encoding fused with the write of keys and values into the paged
+// cache, and causal attention of each token over its sequence's cache.
+//
+// Cache entry layout: K and V each [n_pages][n_kv_heads][page_tokens][head_dim].
+// A sequence (slot) owns a row of `page_table` ([n_slots][max_pages], int32); position
+// p of the sequence lies in page page_table[slot][p / page_tokens] at row
+// p % page_tokens.  A token with slot < 0 is padding: nothing is read or written for it.
+#include "common.cuh"
+
+namespace {
+
+// ----------------------------------------------------------------------------- rotary + store
+
+// For every token and head: rotate pairs (2j, 2j+1), 2j < R, of q (in place) and k by the
+// angle pos * base^(-2j/R), taken from a 32-bit table [max_pos][R/2][2] = (cos, sin):
+//   a' = a cos - b sin ; b' = a sin + b cos            (QStream src/engine.c:216-218)
+// then keep the rotated k and the v in the cache (rope before store: src/engine.c:871-880).
+// The rotation is evaluated in 32-bit and rounded once.  q == nullptr: keys/values only.
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                                  size_t ldq, size_t ldk, size_t ldv,
+                                  int n_heads, int n_kv_heads, int dh, int R,
+                                  const float* __restrict__ cos_sin, int max_pos,
+                                  const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                                  const int32_t* __restrict__ page_table, int max_pages, int page_shift,
+                                  T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                  int32_t* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int slot = tok_slot[t];
+    if (slot < 0) return;
+    const int pos = tok_pos[t];
+    const int head = blockIdx.y;            // [0, n_heads): q; then k heads; then v heads
+    const int page_tokens = 1 << page_shift;
+    const bool rotate = cos_sin != nullptr && R > 0;
+    if (rotate && (pos < 0 || pos >= max_pos)) { if (threadIdx.x == 0) atomicExch(status, 1); return; }
+    const float* cs = rotate ? cos_sin + (size_t)pos * R : nullptr;      // R/2 pairs of (cos, sin)
+
+    size_t cache_row = 0;
+    if (head >= n_heads) {
+        const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
+        if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
+        const int kvh = (head - n_heads) % n_kv_heads;
+        cache_row = (((size_t)page * n_kv_heads + kvh) * page_tokens + (pos & (page_tokens - 1))) * dh;
+    }
+
+    if (head < n_heads) {
+        if (!q || !rotate) return;
+        T* row = q + (size_t)t * ldq + (size_t)head * dh;
+        for (int j = threadIdx.x; 2 * j < R; j += blockDim.x) {
+            const float c = cs[2 * j], s = cs[2 * j + 1];
+            const float a = to_f32(row[2 * j]), b = to_f32(row[2 * j + 1]);
+            row[2 * j] = from_f32<T>(a * c - b * s);
+            row[2 * j + 1] = from_f32<T>(a * s + b * c);
+        }
+    } else if (head < n_heads + n_kv_heads) {
+        const T* row = k + (size_t)t * ldk + (size_t)(head - n_heads) * dh;
+        T* dst = k_cache + cache_row;
+        for (int j = threadIdx.x; 2 * j < dh; j += blockDim.x) {
+            const float a = to_f32(row[2 * j]), b = to_f32(row[2 * j + 1]);
+            if (rotate && 2 * j < R) {
+                const float c = cs[2 * j], s = cs[2 * j + 1];
+                dst[2 * j] = from_f32<T>(a * c - b * s);
+                dst[2 * j + 1] = from_f32<T>(a * s + b * c);
+            } else {
+                dst[2 * j] = row[2 * j];
+                dst[2 * j + 1] = row[2 * j + 1];
+            }
+        }
+    } else {
+        const T* row = v + (size_t)t * ldv + (size_t)(head - n_heads - n_kv_heads) * dh;
+        T* dst = v_cache + cache_row;
+        for (int j = threadIdx.x; j < dh; j += blockDim.x) dst[j] = row[j];
+    }
+}
+
+// ----------------------------------------------------------------------------- attention
+
+// One warp per (token, query head).  Keys are visited 32 at a time in position order:
+// lane l scores key base+l (s = q.k / sqrt(dh), QStream src/engine.c:888-906), the
+// running maximum and sum are updated (softmax with max subtraction,
+// src/kernels_scalar.c:188-213, in its streaming form) and the 32 weighted values are
+// added in key order (src/engine.c:913-922).  Scores, maximum, exponentials, sum and
+// the output accumulator are 32-bit.  The order of the sums depends only on the
+// token's own position, never on the batch or on where the pages lie.
+// Lane l owns output dims l, l+32, ...: NACC = ceil(dh / 32) accumulators.
+template <typename T, int NACC>
+__global__ void __launch_bounds__(128)
+attention_kernel(T* __restrict__ out, const T* __restrict__ q, size_t ldo, size_t ldq,
+                 const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                 const int32_t* __restrict__ page_table, int max_pages, int page_shift,
+                 const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                 int T_tokens, int n_heads, int n_kv_heads, int dh, float scale, int window,
+                 int32_t* __restrict__ status) {
+    extern __shared__ float q_smem[];               // [warps][dh]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps = blockDim.x >> 5;
+    const long long item = (long long)blockIdx.x * warps + warp;
+    if (item >= (long long)T_tokens * n_heads) return;
+    const int t = (int)(item / n_heads), head = (int)(item % n_heads);
+    T* o = out + (size_t)t * ldo + (size_t)head * dh;
+    const int slot = tok_slot[t];
+    if (slot < 0) {                                 // padding: defined output, no cache access
+        for (int d = lane; d < dh; d += 32) o[d] = from_f32<T>(0.f);
+        return;
+    }
+    const int pos = tok_pos[t];
+    const int kvh = head / (n_heads / n_kv_heads);  // QStream src/engine.c:884,889
+    const int page_tokens = 1 << page_shift;
+    const int32_t* pages = page_table + (size_t)slot * max_pages;
+
+    float* qs = q_smem + (size_t)warp * dh;
+    const T* qrow = q + (size_t)t * ldq + (size_t)head * dh;
+    for (int d = lane; d < dh; d += 32) qs[d] = to_f32(qrow[d]);
+    __syncwarp();
+
+    float acc[NACC];
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+
+    for (int base = first; base <= pos; base += 32) {
+        const int key = base + lane;
+        const bool live = key <= pos;
+        float s = -INFINITY;
+        const T* vrow = nullptr;
+        if (live) {
+            const int page = pages[key >> page_shift];
+            if (page < 0) { atomicExch(status, 3); }
+            else {
+                const size_t off = (((size_t)page * n_kv_heads + kvh) * page_tokens + (key & (page_tokens - 1))) * dh;
+                const T* krow = k_cache + off;
+                vrow = v_cache + off;
+                float dot = 0.f;
+                for (int d = 0; d < dh; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
+                s = dot * scale;
+            }
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = live && vrow ? expf(s - m_new) : 0.f;
+        const float alpha = m == -INFINITY ? 0.f : expf(m - m_new);
+        l = l * alpha + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < NACC; ++i) acc[i] *= alpha;
+        const int n_keys = min(32, pos - base + 1);
+        for (int j = 0; j < n_keys; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            const T* vj = reinterpret_cast<const T*>(__shfl_sync(0xffffffffu, (unsigned long long)vrow, j));
+            if (!vj) continue;
+#pragma unroll
+            for (int i = 0; i < NACC; ++i) {
+                const int d = lane + 32 * i;
+                if (d < dh) acc[i] = fmaf(pj, to_f32(vj[d]), acc[i]);
+            }
+        }
+        m = m_new;
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+    for (int i = 0; i < NACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < dh) o[d] = from_f32<T>(acc[i] * inv);
+    }
+}
+
+template <typename T>
+int launch_attention(void* out, const void* q, long long ldo, long long ldq, const void* k_cache,
+                     const void* v_cache, const int32_t* page_table, int max_pages, int page_shift,
+                     const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
+                     int n_kv_heads, int dh, float scale, int window, int32_t* status,
+                     cudaStream_t stream) {
+    const int warps = 4;
+    const long long items = (long long)T_tokens * n_heads;
+    const int blocks = (int)((items + warps - 1) / warps);
+    const size_t smem = (size_t)warps * dh * sizeof(float);
+#define GO(NACC) attention_kernel<T, NACC><<<blocks, warps * 32, smem, stream>>>( \
+        (T*)out, (const T*)q, (size_t)ldo, (size_t)ldq, (const T*)k_cache, (const T*)v_cache, \
+        page_table, max_pages, page_shift, tok_slot, tok_pos, T_tokens, n_heads, n_kv_heads, dh, \
+        scale, window, status)
+    const int nacc = (dh + 31) / 32;
+    if (nacc <= 1) GO(1);
+    else if (nacc <= 2) GO(2);
+    else if (nacc <= 4) GO(4);
+    else if (nacc <= 8) GO(8);
+    else GO(16);
+#undef GO
+    return qs_check_launch("attention");
+}
+
+}  // namespace
+
+QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
+                         long long ldq, long long ldk, long long ldv,
+                         int n_heads, int n_kv_heads, int dh, int R,
+                         const float* cos_sin, int max_pos,
+                         const int32_t* tok_slot, const int32_t* tok_pos,
+                         const int32_t* page_table, int max_pages, int page_tokens,
+                         void* k_cache, void* v_cache, int T_tokens, int32_t* status,
+                         cudaStream_t stream) {
+    if (T_tokens == 0) return QS_OK;
+    QS_REQUIRE(T_tokens > 0 && n_heads >= 0 && n_kv_heads >= 0 && n_heads + n_kv_heads > 0 && dh > 0, "rope_store: bad sizes");
+    QS_REQUIRE(n_kv_heads == 0 || (k && v && k_cache && v_cache), "rope_store: keys and values without a cache to keep them");
+    QS_REQUIRE(dh % 2 == 0, "rope_store: head size %d must be even", dh);
+    QS_REQUIRE(R >= 0 && R % 2 == 0 && R <= dh, "rope_store: rotary width %d must be even and within the head size %d", R, dh);
+    QS_REQUIRE(page_tokens > 0 && (page_tokens & (page_tokens - 1)) == 0, "rope_store: page size %d is no power of two", page_tokens);
+    QS_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope_store: too many heads");
+    int shift = 0;
+    while ((1 << shift) < page_tokens) ++shift;
+    dim3 grid(T_tokens, n_heads + 2 * n_kv_heads);
+    const int threads = dh >= 256 ? 128 : (dh >= 128 ? 64 : 32);
+    if (dtype == QS_F32)
+        rope_store_kernel<float><<<grid, threads, 0, stream>>>((float*)q, (const float*)k, (const float*)v,
+            (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos,
+            page_table, max_pages, shift, (float*)k_cache, (float*)v_cache, status);
+    else if (dtype == QS_BF16)
+        rope_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)q, (const __nv_bfloat16*)k,
+            (const __nv_bfloat16*)v, (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos,
+            tok_slot, tok_pos, page_table, max_pages, shift, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "rope_store: unknown dtype %d", dtype);
+    return qs_check_launch("rope_store");
+}
+
+QS_API int qs_attention(void* out, const void* q, int dtype, long long ldo, long long ldq,
+                        const void* k_cache, const void* v_cache,
+                        const int32_t* page_table, int max_pages, int page_tokens,
+                        const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens,
+                        int n_heads, int n_kv_heads, int dh, float scale, int window,
+                        int32_t* status, cudaStream_t stream) {
+    if (T_tokens == 0) return QS_OK;
+    QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && dh > 0, "attention: bad sizes");
+    QS_REQUIRE(n_heads % n_kv_heads == 0, "attention: %d query heads are no multiple of %d key heads", n_heads, n_kv_heads);
+    QS_REQUIRE(dh <= 512, "attention: head size %d above 512", dh);
+    QS_REQUIRE(page_tokens > 0 && (page_tokens & (page_tokens - 1)) == 0, "attention: page size %d is no power of two", page_tokens);
+    QS_REQUIRE(window >= 0, "attention: negative window");
+    int shift = 0;
+    while ((1 << shift) < page_tokens) ++shift;
+    if (dtype == QS_F32)
+        return launch_attention<float>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift, tok_slot,
+                                       tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window, status, stream);
+    if (dtype == QS_BF16)
+        return launch_attention<__nv_bfloat16>(out, q, ldo, ldq, k_cache, v_cache, page_table, max_pages, shift,
+                                               tok_slot, tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window,
+                                               status, stream);
+    return qs_fail(QS_ERR_INVALID_INPUT, "attention: unknown dtype %d", dtype);
+}

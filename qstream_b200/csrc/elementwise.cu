@@ -1,0 +1,168 @@
+// Error reporting, embedding lookup, LayerNorm, row gather and residual add.
+//
+// Each kernel has a plain reference with the same formula in tests/plain_gptj.py.
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+
+// ----------------------------------------------------------------------------- errors
+
+static thread_local char g_error[512] = "";
+
+int qs_fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int qs_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "%s: %s", what, cudaGetErrorString(e));
+    return QS_OK;
+}
+
+QS_API const char* qs_last_error(void) { return g_error; }
+
+QS_API int qs_abi_version(void) { return 1; }
+
+// ----------------------------------------------------------------------------- embedding
+
+// out[t, :] = table[token[t], :]   (QStream src/engine.c:710-765; no position term).
+// Token ids are checked by the caller; an id outside the table is clamped here so
+// that a bad id can never read outside the table.
+template <typename TO, typename TT>
+__global__ void embedding_kernel(TO* __restrict__ out, const TT* __restrict__ table,
+                                 const int32_t* __restrict__ tokens, int D, int V) {
+    const int t = blockIdx.x;
+    int id = tokens[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const TT* row = table + (size_t)id * D;
+    TO* dst = out + (size_t)t * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = from_f32<TO>(to_f32(row[i]));
+}
+
+QS_API int qs_embedding(void* out, int out_dtype, const void* table, int table_dtype,
+                        const int32_t* tokens, int T, int D, int V, cudaStream_t stream) {
+    if (T == 0) return QS_OK;
+    QS_REQUIRE(T > 0 && D > 0 && V > 0, "embedding: bad sizes T=%d D=%d V=%d", T, D, V);
+    const int threads = D >= 1024 ? 256 : 128;
+#define LAUNCH(TO, TT) embedding_kernel<TO, TT><<<T, threads, 0, stream>>>( \
+        (TO*)out, (const TT*)table, tokens, D, V)
+    if (out_dtype == QS_F32 && table_dtype == QS_F32) LAUNCH(float, float);
+    else if (out_dtype == QS_F32 && table_dtype == QS_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (out_dtype == QS_BF16 && table_dtype == QS_F32) LAUNCH(__nv_bfloat16, float);
+    else if (out_dtype == QS_BF16 && table_dtype == QS_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "embedding: unknown dtype %d/%d", out_dtype, table_dtype);
+#undef LAUNCH
+    return qs_check_launch("embedding");
+}
+
+// ----------------------------------------------------------------------------- LayerNorm
+
+// mean = sum x / D; var = sum (x - mean)^2 / D (two passes); y = (x - mean) / sqrt(var + eps) * w + b
+// (QStream src/kernels_scalar.c:151-171).  Statistics in 32-bit whatever the storage type.
+// One block per row; the row is held in shared memory as 32-bit floats.
+template <typename T>
+__global__ void layernorm_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                 const void* __restrict__ w, int w_dtype,
+                                 const void* __restrict__ b, int b_dtype,
+                                 int D, float eps, size_t ldx, size_t ldo) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const T* src = x + (size_t)blockIdx.x * ldx;
+    T* dst = out + (size_t)blockIdx.x * ldo;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = to_f32(src[i]);
+        row[i] = v;
+        s += v;
+    }
+    const float mean = block_sum(s, scratch) / (float)D;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float d = row[i] - mean;
+        q += d * d;
+    }
+    const float var = block_sum(q, scratch) / (float)D;
+    const float rstd = 1.0f / sqrtf(var + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float y = (row[i] - mean) * rstd * load_as_f32(w, w_dtype, i);
+        if (b) y += load_as_f32(b, b_dtype, i);
+        dst[i] = from_f32<T>(y);
+    }
+}
+
+QS_API int qs_layernorm(void* out, const void* x, int dtype, const void* w, int w_dtype,
+                        const void* b, int b_dtype, int rows, int D, float eps,
+                        long long ldx, long long ldo, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && D > 0, "layernorm: bad sizes rows=%d D=%d", rows, D);
+    const size_t smem = (size_t)D * sizeof(float);
+    QS_REQUIRE(smem <= 200 * 1024, "layernorm: width %d does not fit one block's shared memory (max %d)",
+               D, 200 * 1024 / 4);
+    const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+    cudaError_t e = cudaSuccess;
+    if (dtype == QS_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) layernorm_kernel<float><<<rows, threads, smem, stream>>>(
+            (float*)out, (const float*)x, w, w_dtype, b, b_dtype, D, eps, (size_t)ldx, (size_t)ldo);
+    } else if (dtype == QS_BF16) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) layernorm_kernel<__nv_bfloat16><<<rows, threads, smem, stream>>>(
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)x, w, w_dtype, b, b_dtype, D, eps, (size_t)ldx, (size_t)ldo);
+    } else {
+        return qs_fail(QS_ERR_INVALID_INPUT, "layernorm: unknown dtype %d", dtype);
+    }
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "layernorm: %s", cudaGetErrorString(e));
+    return qs_check_launch("layernorm");
+}
+
+// ----------------------------------------------------------------------------- gather rows
+
+// out[i, :] = x[rows[i], :]: the rows whose logits are wanted, picked before the
+// final norm and the head so that only they pay for the vocabulary projection.
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x,
+                                   const int32_t* __restrict__ rows, int D, size_t ldx) {
+    const T* src = x + (size_t)rows[blockIdx.x] * ldx;
+    T* dst = out + (size_t)blockIdx.x * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+}
+
+QS_API int qs_gather_rows(void* out, const void* x, int dtype, const int32_t* rows, int n, int D,
+                          long long ldx, cudaStream_t stream) {
+    if (n == 0) return QS_OK;
+    QS_REQUIRE(n > 0 && D > 0, "gather_rows: bad sizes n=%d D=%d", n, D);
+    if (dtype == QS_F32) gather_rows_kernel<float><<<n, 256, 0, stream>>>((float*)out, (const float*)x, rows, D, (size_t)ldx);
+    else if (dtype == QS_BF16) gather_rows_kernel<__nv_bfloat16><<<n, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, rows, D, (size_t)ldx);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "gather_rows: unknown dtype %d", dtype);
+    return qs_check_launch("gather_rows");
+}
+
+// ----------------------------------------------------------------------------- residual add
+
+// out = a + b (+ c), summed in 32-bit and rounded once.  For parts that cannot add
+// the residual in their last kernel.
+template <typename T>
+__global__ void add_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b,
+                           const T* __restrict__ c, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = to_f32(a[i]) + to_f32(b[i]);
+        if (c) v += to_f32(c[i]);
+        out[i] = from_f32<T>(v);
+    }
+}
+
+QS_API int qs_add(void* out, const void* a, const void* b, const void* c, int dtype, long long n,
+                  cudaStream_t stream) {
+    if (n == 0) return QS_OK;
+    QS_REQUIRE(n > 0, "add: bad size %lld", n);
+    const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    if (dtype == QS_F32) add_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (const float*)a, (const float*)b, (const float*)c, (size_t)n);
+    else if (dtype == QS_BF16) add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (const __nv_bfloat16*)c, (size_t)n);
+    else return qs_fail(QS_ERR_INVALID_INPUT, "add: unknown dtype %d", dtype);
+    return qs_check_launch("add");
+}

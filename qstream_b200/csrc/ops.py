@@ -1,0 +1,241 @@
+"""Python face of the kernel library: one function per `extern "C"` entry point.
+
+Tensors are torch CUDA tensors used as typed device buffers; every launch goes on
+torch's current stream, so the calls can be captured in a CUDA graph.  There is no
+other implementation behind these functions: if the library cannot be built or
+loaded, or a tensor is not on a CUDA device, the call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..errors import QsError, QStreamError
+from . import build as _build
+
+F32, BF16 = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
+ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "gelu_new": ACT_GELU_TANH, "gelu": ACT_GELU_ERF}
+
+_lib = None
+
+_SIGNATURES = {
+    "qs_abi_version": ([], c_int),
+    "qs_embedding": ([c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
+    "qs_layernorm": ([c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                      c_longlong, c_longlong, c_void_p], c_int),
+    "qs_gather_rows": ([c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p], c_int),
+    "qs_add": ([c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p], c_int),
+    "qs_linear_simt": ([c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+                        c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p], c_int),
+    "qs_rope_store": ([c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong,
+                       c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                       c_void_p, c_void_p, c_int, c_void_p, c_void_p], c_int),
+    "qs_attention": ([c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                      c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                      c_void_p], c_int),
+    "qs_argmax": ([c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p], c_int),
+    "qs_repeat_penalty": ([c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_float, c_void_p], c_int),
+    "qs_sample": ([c_void_p, c_void_p, c_int, c_int, c_longlong, c_float, c_int, c_float, c_void_p, c_void_p], c_int),
+}
+
+
+def library():
+    """The loaded kernel library; built on first use."""
+    global _lib
+    if _lib is None:
+        path = _build.build()
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as e:
+            raise QStreamError(QsError.INTERNAL, f"cannot load {path}: {e}") from None
+        lib.qs_last_error.restype = ctypes.c_char_p
+        lib.qs_last_error.argtypes = []
+        for name, (argtypes, restype) in _SIGNATURES.items():
+            if not hasattr(lib, name):
+                continue                    # optional entry points are bound by their own modules
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
+        _lib = lib
+    return _lib
+
+
+def bind(name: str, argtypes, restype=c_int):
+    """Bind one more entry point (used by modules that own further kernels)."""
+    lib = library()
+    try:
+        fn = getattr(lib, name)
+    except AttributeError:
+        raise QStreamError(QsError.INTERNAL, f"the kernel library has no entry point '{name}'") from None
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        detail = library().qs_last_error().decode(errors="replace")
+        try:
+            code = QsError(rc)
+        except ValueError:
+            code = QsError.INTERNAL
+        raise QStreamError(code, detail)
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise QStreamError(QsError.INVALID_INPUT, f"kernels take float32 or bfloat16, got {t.dtype}")
+
+
+def ptr(t) -> int | None:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise QStreamError(QsError.INVALID_INPUT, "kernels run on CUDA tensors only; there is no CPU path")
+    return t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _rows(t: torch.Tensor):
+    """(rows, width, row stride) of a 2-D tensor whose rows are contiguous."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise QStreamError(QsError.INVALID_INPUT, f"need a 2-D tensor with contiguous rows, got "
+                           f"shape {tuple(t.shape)} strides {t.stride()}")
+    return t.shape[0], t.shape[1], t.stride(0)
+
+
+def _int32(t: torch.Tensor, what: str):
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise QStreamError(QsError.INVALID_INPUT, f"{what} must be a contiguous int32 tensor")
+    return ptr(t)
+
+
+# ------------------------------------------------------------------------------- wrappers
+
+def embedding(table: torch.Tensor, tokens: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    V, D = table.shape
+    T = tokens.numel()
+    out = torch.empty((T, D), dtype=out_dtype, device=table.device)
+    check(library().qs_embedding(ptr(out), dtype_code(out), ptr(table), dtype_code(table),
+                                 _int32(tokens, "tokens"), T, D, V, stream()))
+    return out
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float, out=None) -> torch.Tensor:
+    rows, D, ldx = _rows(x)
+    if out is None:
+        out = torch.empty((rows, D), dtype=x.dtype, device=x.device)
+    _, _, ldo = _rows(out)
+    if weight.numel() != D or (bias is not None and bias.numel() != D):
+        raise QStreamError(QsError.INVALID_INPUT, f"layernorm: width {D} but weight {tuple(weight.shape)}")
+    check(library().qs_layernorm(ptr(out), ptr(x), dtype_code(x), ptr(weight), dtype_code(weight),
+                                 ptr(bias), dtype_code(bias) if bias is not None else 0, rows, D,
+                                 float(eps), ldx, ldo, stream()))
+    return out
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    _, D, ldx = _rows(x)
+    n = rows.numel()
+    out = torch.empty((n, D), dtype=x.dtype, device=x.device)
+    check(library().qs_gather_rows(ptr(out), ptr(x), dtype_code(x), _int32(rows, "rows"), n, D, ldx, stream()))
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor, c=None) -> torch.Tensor:
+    for t in (b, c):
+        if t is not None and (t.shape != a.shape or t.dtype != a.dtype or not t.is_contiguous()):
+            raise QStreamError(QsError.INVALID_INPUT, "add: operands differ in shape, type or layout")
+    if not a.is_contiguous():
+        raise QStreamError(QsError.INVALID_INPUT, "add: operands must be contiguous")
+    out = torch.empty_like(a)
+    check(library().qs_add(ptr(out), ptr(a), ptr(b), ptr(c), dtype_code(a), a.numel(), stream()))
+    return out
+
+
+def linear_simt(x, weight, bias=None, activation=None, residuals=(), out_dtype=None) -> torch.Tensor:
+    """act(x W^T + bias) + residuals, accumulated in true 32-bit on the CUDA cores."""
+    M, K, lda = _rows(x)
+    N, K2 = weight.shape
+    if K2 != K or not weight.is_contiguous():
+        raise QStreamError(QsError.INVALID_INPUT, f"linear: x is [{M}, {K}] but weight is {tuple(weight.shape)}")
+    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    res = list(residuals) + [None, None]
+    ldr = N
+    for r in res[:2]:
+        if r is not None:
+            if r.shape != (M, N) or r.dtype != x.dtype or r.stride(1) != 1:
+                raise QStreamError(QsError.INVALID_INPUT, "linear: residual differs in shape or type")
+            ldr = r.stride(0)
+    if len(residuals) > 2 or (len(residuals) == 2 and res[0].stride(0) != res[1].stride(0)):
+        raise QStreamError(QsError.INVALID_INPUT, "linear: at most two residuals of one layout")
+    check(library().qs_linear_simt(ptr(out), dtype_code(out), ptr(x), dtype_code(x), ptr(weight),
+                                   dtype_code(weight), ptr(bias), dtype_code(bias) if bias is not None else 0,
+                                   ACTIVATIONS[activation], ptr(res[0]), ptr(res[1]), M, N, K, lda, N, ldr,
+                                   stream()))
+    return out
+
+
+def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_slot, tok_pos,
+               page_table, page_tokens, k_cache, v_cache, status) -> None:
+    """Rotate q (in place) and k, and write k and v into the paged cache entry.
+    k = v = None (n_kv_heads = 0): rotate q only."""
+    ref = k if k is not None else q
+    T = ref.shape[0]
+    max_pos = cos_sin.shape[0] if cos_sin is not None else 0
+    check(library().qs_rope_store(
+        ptr(q), ptr(k), ptr(v), dtype_code(ref), q.stride(0) if q is not None else 0,
+        k.stride(0) if k is not None else 0, v.stride(0) if v is not None else 0,
+        n_heads if q is not None else 0, n_kv_heads, head_dim, rotary_dim if cos_sin is not None else 0,
+        ptr(cos_sin), max_pos, _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
+        _int32(page_table, "page_table"), page_table.shape[1], page_tokens, ptr(k_cache), ptr(v_cache), T,
+        ptr(status), stream()))
+
+
+def attention(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table,
+              page_tokens, k_cache, v_cache, status) -> torch.Tensor:
+    """Causal attention of every token over its sequence's cache (generic kernel)."""
+    T = q.shape[0]
+    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    check(library().qs_attention(
+        ptr(out), ptr(q), dtype_code(q), out.stride(0), q.stride(0), ptr(k_cache), ptr(v_cache),
+        _int32(page_table, "page_table"), page_table.shape[1], page_tokens, _int32(tok_slot, "tok_slot"),
+        _int32(tok_pos, "tok_pos"), T, n_heads, n_kv_heads, head_dim, float(scale), int(window),
+        ptr(status), stream()))
+    return out
+
+
+def argmax(logits: torch.Tensor, out=None) -> torch.Tensor:
+    rows, V, ld = _rows(logits)
+    if logits.dtype != torch.float32:
+        raise QStreamError(QsError.INVALID_INPUT, "argmax: logits must be float32")
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    check(library().qs_argmax(ptr(out), ptr(logits), rows, V, ld, stream()))
+    return out
+
+
+def repeat_penalty(logits, recent, n_recent, penalty: float) -> None:
+    rows, V, ld = _rows(logits)
+    check(library().qs_repeat_penalty(ptr(logits), rows, V, ld, _int32(recent, "recent"), recent.shape[1],
+                                      _int32(n_recent, "n_recent"), float(penalty), stream()))
+
+
+def sample(logits, temperature: float, top_k: int, top_p: float, draws, out=None) -> torch.Tensor:
+    rows, V, ld = _rows(logits)
+    if logits.dtype != torch.float32 or draws.dtype != torch.float32 or draws.numel() != rows:
+        raise QStreamError(QsError.INVALID_INPUT, "sample: logits and draws must be float32, one draw per row")
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    check(library().qs_sample(ptr(out), ptr(logits), rows, V, ld, float(temperature), int(top_k),
+                              float(top_p), ptr(draws), stream()))
+    return out

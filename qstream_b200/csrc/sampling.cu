@@ -1,0 +1,243 @@
+// Sampling on the device: argmax, repeat penalty, temperature, top-k, top-p and the
+// inverse-CDF draw, with the meanings of QStream's src/sampling.c.
+//
+// One block works on one row of 32-bit logits [V].  Nothing is written to the logits
+// by the sampler itself (the repeat penalty is a kernel of its own); filters are kept
+// as thresholds.  All sums are taken in a fixed order, so a row's token depends only
+// on its logits, its options and its draw r, not on the other rows.
+#include "common.cuh"
+
+namespace {
+
+constexpr int SAMPLE_THREADS = 1024;
+
+// Monotone map of a float to an unsigned key (larger float -> larger key).
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = -INFINITY;
+        for (int i = 0; i < n_warps; ++i) t = fmaxf(t, scratch[i]);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Greedy: strict '>' scan, so the lowest index wins ties (src/sampling.c:214-224).
+__global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict__ logits,
+                              int V, size_t ld) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i];
+        if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
+    }
+    // NaN never compares greater; a row of NaN ends at its first visited index.
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int n_warps = (blockDim.x + 31) >> 5;
+        for (int w = 1; w < n_warps; ++w) {
+            const float ov = best_v[w];
+            const int oi = best_i[w];
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+// Divide positive and multiply negative logits of the recent tokens by the penalty,
+// once per occurrence, in the order of the window (src/sampling.c:59-74).
+__global__ void repeat_penalty_kernel(float* __restrict__ logits, int V, size_t ld,
+                                      const int32_t* __restrict__ recent, int window,
+                                      const int32_t* __restrict__ n_recent, float penalty) {
+    const int row = blockIdx.x;
+    if (threadIdx.x != 0) return;
+    float* x = logits + (size_t)row * ld;
+    const int n = min(n_recent[row], window);
+    for (int i = 0; i < n; ++i) {
+        const int t = recent[(size_t)row * window + i];
+        if (t < 0 || t >= V) continue;
+        x[t] = x[t] > 0.f ? x[t] / penalty : x[t] * penalty;
+    }
+}
+
+// Temperature, top-k, top-p, softmax, inverse-CDF (src/sampling.c:227-250), for a
+// temperature >= 0.01 (the caller sends greedy rows to argmax_kernel).
+//   y = x / T (unless T == 1)                                              (:50-56)
+//   top-k: y below the k-th largest is dropped, ties at it stay            (:77-118)
+//   top-p: of softmax(y), in descending order (equal values: lower index first), keep
+//          through the first element whose cumulative probability exceeds p (:121-175)
+//   draw: first index with cumulative probability >= r; if none, the last kept (:199-211)
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(int32_t* __restrict__ out, const float* __restrict__ logits, int V, size_t ld,
+              float temperature, int top_k, float top_p, const float* __restrict__ draws) {
+    __shared__ float scratch[33];
+    __shared__ float chunk_sum[SAMPLE_THREADS];
+    __shared__ int chunk_ties[SAMPLE_THREADS];
+    __shared__ int result;
+    const float* x = logits + (size_t)blockIdx.x * ld;
+    const float inv_t = temperature == 1.0f ? 1.0f : 1.0f / temperature;
+    const int tid = threadIdx.x;
+
+    // the k-th largest key
+    uint32_t k_key = 0;                              // keep everything
+    if (top_k > 0 && top_k < V) {
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t trial = k_key | (1u << bit);
+            float cnt = 0.f;
+            for (int i = tid; i < V; i += blockDim.x) cnt += order_key(x[i] * inv_t) >= trial ? 1.f : 0.f;
+            if (block_sum(cnt, scratch) >= (float)top_k) k_key = trial;
+        }
+    }
+
+    float mx = -INFINITY;
+    for (int i = tid; i < V; i += blockDim.x) mx = fmaxf(mx, x[i] * inv_t);
+    mx = block_max(mx, scratch);
+
+    float z = 0.f;
+    for (int i = tid; i < V; i += blockDim.x) {
+        const float y = x[i] * inv_t;
+        if (order_key(y) >= k_key) z += expf(y - mx);
+    }
+    z = block_sum(z, scratch);
+
+    // top-p: the key of the element at which the cumulative sum first exceeds p, and how
+    // many of the elements equal to it (in index order) are kept
+    uint32_t p_key = 0;
+    int ties_kept = 0x7fffffff;
+    if (top_p > 0.f && top_p < 1.f && z > 0.f) {
+        const float limit = top_p * z;
+        for (int bit = 31; bit >= 0; --bit) {
+            const uint32_t trial = p_key | (1u << bit);
+            float s = 0.f;
+            for (int i = tid; i < V; i += blockDim.x) {
+                const float y = x[i] * inv_t;
+                const uint32_t key = order_key(y);
+                if (key >= k_key && key >= trial) s += expf(y - mx);
+            }
+            if (block_sum(s, scratch) > limit) p_key = trial;
+        }
+        float above = 0.f, at = 0.f;
+        for (int i = tid; i < V; i += blockDim.x) {
+            const float y = x[i] * inv_t;
+            const uint32_t key = order_key(y);
+            if (key >= k_key && key > p_key) above += expf(y - mx);
+            if (key >= k_key && key == p_key) at = expf(y - mx);
+        }
+        above = block_sum(above, scratch);
+        at = block_max(at, scratch);
+        ties_kept = 1;
+        if (at > 0.f) while (above + (float)ties_kept * at <= limit && ties_kept < V) ++ties_kept;
+    }
+    const uint32_t keep_key = p_key > k_key ? p_key : k_key;   // keys below this are dropped
+
+    // chunked pass in index order: every thread owns a contiguous range
+    const bool tie_rule = ties_kept != 0x7fffffff;
+    const int per = (V + blockDim.x - 1) / blockDim.x;
+    const int c0 = min(V, tid * per), c1 = min(V, c0 + per);
+    int local_ties = 0;
+    if (tie_rule)
+        for (int i = c0; i < c1; ++i) local_ties += order_key(x[i] * inv_t) == p_key ? 1 : 0;
+    chunk_ties[tid] = local_ties;
+    if (tid == 0) result = 0x7fffffff;
+    __syncthreads();
+    int ties_before = 0;                              // elements equal to the cut-off value before this chunk
+    if (tie_rule)
+        for (int j = 0; j < tid; ++j) ties_before += chunk_ties[j];
+
+    // weight of element i in the final distribution (0 if filtered); `rank` counts ties
+    auto weight = [&](int i, int& rank) -> float {
+        const float y = x[i] * inv_t;
+        const uint32_t key = order_key(y);
+        if (key < keep_key) return 0.f;
+        if (tie_rule && key == p_key && rank++ >= ties_kept) return 0.f;
+        return expf(y - mx);
+    };
+
+    float local = 0.f;
+    {
+        int rank = ties_before;
+        for (int i = c0; i < c1; ++i) local += weight(i, rank);
+    }
+    chunk_sum[tid] = local;
+    __syncthreads();
+    if (tid == 0) {                                   // ordered prefix: chunk_sum[j] becomes the sum before chunk j
+        float run = 0.f;
+        for (int j = 0; j < blockDim.x; ++j) { const float c = chunk_sum[j]; chunk_sum[j] = run; run += c; }
+        scratch[0] = run;
+    }
+    __syncthreads();
+    const float total = scratch[0];
+    const float target = draws[blockIdx.x] * total;
+    const float before = chunk_sum[tid];
+    // The first index whose cumulative weight reaches the target lies in the chunk with
+    // before < target <= before + local; the walk below repeats the additions of `local`
+    // exactly, so that chunk finds it.
+    if (c0 < c1 && before + local >= target && (before < target || target <= 0.f)) {
+        float part = 0.f;
+        int rank = ties_before;
+        for (int i = c0; i < c1; ++i) {
+            const float wgt = weight(i, rank);
+            if (wgt == 0.f) continue;
+            part += wgt;
+            if (before + part >= target) { atomicMin(&result, i); break; }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int r = result;
+        if (r == 0x7fffffff) {                        // empty or non-finite distribution: last kept, else 0
+            r = 0;
+            int rank = 0;
+            for (int i = 0; i < V; ++i) if (weight(i, rank) > 0.f) r = i;
+        }
+        out[blockIdx.x] = r;
+    }
+}
+
+}  // namespace
+
+QS_API int qs_argmax(int32_t* out, const float* logits, int rows, int V, long long ld, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && V > 0 && ld >= V, "argmax: bad sizes rows=%d V=%d ld=%lld", rows, V, ld);
+    argmax_kernel<<<rows, V >= 4096 ? 1024 : 256, 0, stream>>>(out, logits, V, (size_t)ld);
+    return qs_check_launch("argmax");
+}
+
+QS_API int qs_repeat_penalty(float* logits, int rows, int V, long long ld, const int32_t* recent,
+                             int window, const int32_t* n_recent, float penalty, cudaStream_t stream) {
+    if (rows == 0 || penalty <= 1.0f) return QS_OK;
+    QS_REQUIRE(rows > 0 && V > 0 && window > 0, "repeat_penalty: bad sizes");
+    repeat_penalty_kernel<<<rows, 32, 0, stream>>>(logits, V, (size_t)ld, recent, window, n_recent, penalty);
+    return qs_check_launch("repeat_penalty");
+}
+
+QS_API int qs_sample(int32_t* out, const float* logits, int rows, int V, long long ld, float temperature,
+                     int top_k, float top_p, const float* draws, cudaStream_t stream) {
+    if (rows == 0) return QS_OK;
+    QS_REQUIRE(rows > 0 && V > 0 && ld >= V, "sample: bad sizes rows=%d V=%d ld=%lld", rows, V, ld);
+    QS_REQUIRE(temperature >= 0.01f, "sample: temperature %g is greedy; use argmax", (double)temperature);
+    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(out, logits, V, (size_t)ld, temperature, top_k, top_p, draws);
+    return qs_check_launch("sample");
+}

@@ -1,0 +1,7 @@
+"""The engine: model assembly, step function and generation loop."""
+from .model import CausalLM, declared_tensors, load_model, resolve_dtype
+from .step import Engine, StepBatch, StepContext
+from .generate import GenerationResult, Generator, plan_batches
+
+__all__ = ["CausalLM", "declared_tensors", "load_model", "resolve_dtype", "Engine", "StepBatch",
+           "StepContext", "GenerationResult", "Generator", "plan_batches"]

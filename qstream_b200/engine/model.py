@@ -1,0 +1,166 @@
+"""The model: parts built from a `ModelSpec` and run in the order of its schedule.
+
+Nothing here names an architecture.  The spec lists the layers (each a `BlockSpec`)
+and the schedule (which layer runs when, against which cache entry); the part
+registries turn specs into parts; the loader binds tensors by the names the specs
+carry.  The forward pass is QStream's `qsf_forward` (src/engine.c:694-1247) for a
+whole batch of tokens: embedding, the layers, then final norm and head for the rows
+whose logits are wanted only (the reference runs the head for every prompt token,
+src/engine.c:1289-1295).
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Mapping
+
+import torch
+
+from ..cache import KvNeed, StateNeed
+from ..config import ModelSpec, load_config
+from ..csrc import ops
+from ..errors import QsError, QStreamError
+from ..parts import Runtime, build_block, part_class
+from ..parts.linear import linear
+from ..weights.loader import TensorDecl, bind_tensors, open_checkpoint
+from ..weights.random_init import InitScales, random_tensors
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+          "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    try:
+        return DTYPES[dtype]
+    except KeyError:
+        raise QStreamError(QsError.INVALID_INPUT, f"dtype {dtype!r}: want bfloat16 or float32") from None
+
+
+def _part_declarations(spec: ModelSpec):
+    """Yield (part spec, {own name: TensorDecl}) for every part that holds tensors."""
+    yield spec.embedding, {"weight": TensorDecl((spec.embedding.vocab_size, spec.embedding.width))}
+    for block in spec.layers:
+        for role, ps in (("mixer", block.mixer), ("feed_forward", block.ffn),
+                         *(("norm", n) for n in block.norms.values())):
+            yield ps, part_class(role, ps.kind).declare(ps)
+    yield spec.final_norm, part_class("norm", spec.final_norm.kind).declare(spec.final_norm)
+    head = {} if spec.head.tied else {"weight": TensorDecl((spec.head.vocab_size, spec.head.width))}
+    if spec.head.bias:
+        head["bias"] = TensorDecl((spec.head.vocab_size,), "bias")
+    yield spec.head, head
+
+
+def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
+    """Checkpoint name -> declaration, for every tensor the model holds, in model order."""
+    out: dict[str, TensorDecl] = {}
+    for ps, decls in _part_declarations(spec):
+        for own, decl in decls.items():
+            try:
+                name = ps.names[own]
+            except KeyError:
+                raise QStreamError(QsError.INVALID_MODEL,
+                                   f"{type(ps).__name__} gives no checkpoint name for its tensor '{own}'") from None
+            if name in out and out[name] != decl:
+                raise QStreamError(QsError.INVALID_MODEL, f"tensor '{name}' is declared with two shapes")
+            out[name] = decl
+    return out
+
+
+class CausalLM:
+    """Parts, weights and the forward pass of one model."""
+
+    def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], dtype, device, config=None):
+        self.spec = spec
+        self.config = config
+        self.runtime = Runtime(dtype=resolve_dtype(dtype), device=torch.device(device))
+        self.vocab_size = spec.vocab_size
+
+        def tensors_of(part_spec, decls):
+            return {own: tensors[part_spec.names[own]] for own in decls}
+
+        self.wte = tensors[spec.embedding.names["weight"]]
+        self.blocks = [build_block(b, tensors_of, self.runtime) for b in spec.layers]
+        norm_cls = part_class("norm", spec.final_norm.kind)
+        self.final_norm = norm_cls(spec.final_norm, tensors_of(spec.final_norm, norm_cls.declare(spec.final_norm)),
+                                   self.runtime)
+        self.head_weight = self.wte if spec.head.tied else tensors[spec.head.names["weight"]]
+        self.head_bias = tensors[spec.head.names["bias"]] if spec.head.bias else None
+        self._check_schedule()
+        self.n_parameters = sum(t.numel() for t in {id(t): t for t in tensors.values()}.values())
+        self.weight_bytes = sum(t.numel() * t.element_size() for t in {id(t): t for t in tensors.values()}.values())
+
+    # ------------------------------------------------------------------ making a model
+    @classmethod
+    def from_folder(cls, folder, dtype="bfloat16", device="cuda", allow_mmap=True, verbose=0):
+        """config.json chooses the architecture; *.safetensors give the weights."""
+        config = load_config(folder)
+        spec = config.model_spec()
+        files = open_checkpoint(folder, allow_mmap)
+        try:
+            tensors = bind_tensors(files, declared_tensors(spec), resolve_dtype(dtype), device,
+                                   getattr(config, "ignored_tensor_suffixes", ()))
+        finally:
+            for f in files:
+                f.close()
+        return cls(spec, tensors, dtype, device, config)
+
+    @classmethod
+    def random(cls, config, seed=0, dtype="bfloat16", device="cuda", scales: InitScales = InitScales()):
+        """Random weights made on the device, without a model folder."""
+        spec = config.model_spec()
+        tensors = random_tensors(declared_tensors(spec), seed, resolve_dtype(dtype), device, scales)
+        return cls(spec, tensors, dtype, device, config)
+
+    # ------------------------------------------------------------------ what the cache must hold
+    def _check_schedule(self):
+        writers = {}
+        for i, run in enumerate(self.spec.schedule):
+            if not 0 <= run.layer < len(self.blocks):
+                raise QStreamError(QsError.INVALID_MODEL, f"schedule entry {i} names layer {run.layer}")
+            mixer = self.blocks[run.layer].mixer
+            if mixer.kv_need() is not None or mixer.state_need() is not None:
+                if run.cache in writers:
+                    raise QStreamError(QsError.INVALID_MODEL,
+                                       f"schedule entries {writers[run.cache]} and {i} both write cache entry {run.cache}")
+                writers[run.cache] = i
+        for i, run in enumerate(self.spec.schedule):
+            spec = self.blocks[run.layer].mixer.spec
+            if getattr(spec, "shares_cache", False):
+                if run.cache not in writers or writers[run.cache] > i:
+                    raise QStreamError(QsError.INVALID_MODEL,
+                                       f"schedule entry {i} reads cache entry {run.cache} before any layer wrote it")
+
+    def kv_needs(self) -> dict[int, KvNeed]:
+        out = {}
+        for run in self.spec.schedule:
+            need = self.blocks[run.layer].mixer.kv_need()
+            if need is not None:
+                out[run.cache] = need
+        return out
+
+    def state_needs(self) -> dict[int, StateNeed]:
+        out = {}
+        for run in self.spec.schedule:
+            need = self.blocks[run.layer].mixer.state_need()
+            if need is not None:
+                out[run.cache] = need
+        return out
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, step) -> torch.Tensor | None:
+        """Run the step's tokens through every scheduled layer; return float32 logits
+        [n_want, vocab] of the wanted rows (None if none is wanted)."""
+        b = step.batch
+        x = ops.embedding(self.wte, b.tokens, self.runtime.dtype)
+        for run in self.spec.schedule:
+            x = self.blocks[run.layer].forward(x, step, run.cache)
+        if b.n_want == 0:
+            return None
+        rows = ops.gather_rows(x, b.want_rows)
+        z = self.final_norm.forward(rows)
+        return linear(z, self.head_weight, self.head_bias, out_dtype=torch.float32)
+
+
+def load_model(folder, dtype="bfloat16", device="cuda", **kw) -> CausalLM:
+    if not Path(folder).is_dir():
+        raise QStreamError(QsError.FILE_NOT_FOUND, f"model folder {folder}")
+    return CausalLM.from_folder(folder, dtype, device, **kw)

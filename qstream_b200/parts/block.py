@@ -1,0 +1,67 @@
+"""How a layer's parts are wired: the arrangements.
+
+"parallel": h = norm(x); x + mixer(h) + ffn(h), one norm, both branches read h.  The
+reference engine runs the "sequential" form (x += mixer(norm_1 x); x += ffn(norm_2 x),
+QStream src/engine.c:936-948,1173-1174); both are here, built from the same parts.
+The residual sum is taken in 32-bit inside the last kernel of the branch that ends
+the layer.
+"""
+from __future__ import annotations
+
+from ..errors import QsError, QStreamError
+from .base import Part, part_class, register
+
+
+class Arrangement(Part):
+    role = "arrangement"
+    norm_names: tuple = ()
+
+    def __init__(self, spec, parts, runtime):
+        super().__init__(spec, {}, runtime)
+        self.mixer = parts["mixer"]
+        self.ffn = parts["ffn"]
+        self.norms = parts["norms"]
+        missing = [n for n in self.norm_names if n not in self.norms]
+        if missing:
+            raise QStreamError(QsError.INVALID_MODEL,
+                               f"arrangement '{spec.arrangement}' needs the norms {self.norm_names}, "
+                               f"the layer lacks {missing}")
+
+    def forward(self, x, step, cache_id):
+        raise NotImplementedError
+
+
+class ParallelBlock(Arrangement):
+    norm_names = ("input",)
+
+    def forward(self, x, step, cache_id):
+        h = self.norms["input"].forward(x)
+        a = self.mixer.forward(h, step, cache_id)
+        return self.ffn.forward(h, step, residuals=(x, a))
+
+
+class SequentialBlock(Arrangement):
+    norm_names = ("input", "post_mixer")
+
+    def forward(self, x, step, cache_id):
+        x = self.mixer.forward(self.norms["input"].forward(x), step, cache_id, residuals=(x,))
+        return self.ffn.forward(self.norms["post_mixer"].forward(x), step, residuals=(x,))
+
+
+register("arrangement", "parallel", ParallelBlock)
+register("arrangement", "sequential", SequentialBlock)
+
+
+def build_block(spec, tensors_of, runtime):
+    """Build one layer from its `BlockSpec`.  `tensors_of(part_spec, declaration)` returns
+    the part's tensors by the part's own names."""
+    def make(role, part_spec):
+        cls = part_class(role, part_spec.kind)
+        return cls(part_spec, tensors_of(part_spec, cls.declare(part_spec)), runtime)
+
+    parts = {
+        "mixer": make("mixer", spec.mixer),
+        "ffn": make("feed_forward", spec.ffn),
+        "norms": {name: make("norm", ns) for name, ns in spec.norms.items()},
+    }
+    return part_class("arrangement", spec.arrangement)(spec, parts, runtime)

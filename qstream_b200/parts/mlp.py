@@ -1,0 +1,36 @@
+"""Dense feed-forward: up projection + bias, activation, down projection + bias
+(QStream src/engine.c:1150-1170; the activation's tanh form src/kernels_scalar.c:135-142,
+the erf form is GPT-J's 'gelu').  The activation runs on the 32-bit accumulator of the
+up projection; residuals are added on the accumulator of the down projection."""
+from __future__ import annotations
+
+from ..csrc import ops
+from ..errors import QsError, QStreamError
+from ..weights.loader import TensorDecl
+from .base import FeedForward, register
+from .linear import linear
+
+
+class Mlp(FeedForward):
+    @classmethod
+    def declare(cls, spec):
+        d = {"up": TensorDecl((spec.inner, spec.width)), "down": TensorDecl((spec.width, spec.inner))}
+        if spec.bias:
+            d["up_bias"] = TensorDecl((spec.inner,), "bias")
+            d["down_bias"] = TensorDecl((spec.width,), "bias")
+        return d
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        if spec.activation not in ops.ACTIVATIONS:
+            raise QStreamError(QsError.UNSUPPORTED_ARCH, f"activation '{spec.activation}' has no kernel")
+        self.up, self.down = tensors["up"], tensors["down"]
+        self.up_bias = tensors.get("up_bias") if spec.bias else None
+        self.down_bias = tensors.get("down_bias") if spec.bias else None
+
+    def forward(self, h, step, residuals=()):
+        g = linear(h, self.up, self.up_bias, activation=self.spec.activation)
+        return linear(g, self.down, self.down_bias, residuals=residuals)
+
+
+register("feed_forward", "mlp", Mlp)

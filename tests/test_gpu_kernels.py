@@ -1,0 +1,256 @@
+"""Each kernel alone against a plain float64 reference, at sizes other than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gptj as P
+from qstream_b200.csrc import ops
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=1e-4) if dtype == "float32" else dict(atol=2e-2, rtol=2e-2)
+
+
+def dev(a, dtype=None):
+    t = torch.as_tensor(a)
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def f64(t):
+    return t.detach().cpu().to(torch.float64).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(37, 50, generator=g).to(DT[dtype])
+    toks = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32)
+    out = ops.embedding(table.cuda(), toks.cuda(), DT[dtype])
+    assert torch.equal(out.cpu(), table[toks.long()])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("D,eps,wdtype", [(50, 1e-5, None), (4096, 1e-6, "float32"), (6000, 1e-3, None), (17, 1e-5, None)])
+def test_layernorm(dtype, D, eps, wdtype):
+    g = torch.Generator().manual_seed(D)
+    x = (torch.randn(7, D, generator=g) * 3 + 1.5).to(DT[dtype])
+    wd = DT[wdtype or dtype]
+    w = (1 + 0.2 * torch.randn(D, generator=g)).to(wd)
+    b = (0.1 * torch.randn(D, generator=g)).to(wd)
+    ref = P.layer_norm(f64(x), f64(w), f64(b), eps)
+    got = ops.layernorm(x.cuda(), w.cuda(), b.cuda(), eps)
+    np.testing.assert_allclose(f64(got), ref, **tol(dtype))
+    got = ops.layernorm(x.cuda(), w.cuda(), None, eps)
+    np.testing.assert_allclose(f64(got), P.layer_norm(f64(x), f64(w), None, eps), **tol(dtype))
+
+
+@pytest.mark.parametrize("adt,wdt,cdt", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
+                                         ("bfloat16", "bfloat16", "float32"), ("bfloat16", "float32", "bfloat16"),
+                                         ("float32", "bfloat16", "float32")])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 70, 33), (64, 64, 16), (65, 130, 100), (3, 200, 257)])
+def test_linear_simt(adt, wdt, cdt, M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + N + K)
+    x = torch.randn(M, K, generator=g).to(DT[adt])
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(DT[wdt])
+    bias = torch.randn(N, generator=g).to(DT[wdt])
+    r1 = torch.randn(M, N, generator=g).to(DT[adt])
+    r2 = torch.randn(M, N, generator=g).to(DT[adt])
+    t = tol("float32" if cdt == "float32" and adt == "float32" else cdt)
+    for act, fn in ((None, lambda u: u), ("gelu_new", P.gelu_new), ("gelu", P.gelu_erf)):
+        ref = fn(f64(x) @ f64(w).T + f64(bias)) + f64(r1) + f64(r2)
+        got = ops.linear_simt(x.cuda(), w.cuda(), bias.cuda(), act, (r1.cuda(), r2.cuda()), DT[cdt])
+        assert got.dtype == DT[cdt]
+        np.testing.assert_allclose(f64(got), ref, **t)
+    got = ops.linear_simt(x.cuda(), w.cuda())
+    np.testing.assert_allclose(f64(got), f64(x) @ f64(w).T, **tol(adt))
+
+
+def test_linear_simt_row_does_not_depend_on_batch():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(70, 300, generator=g).cuda()
+    w = torch.randn(90, 300, generator=g).cuda()
+    whole = ops.linear_simt(x, w)
+    for r in (0, 13, 69):
+        assert torch.equal(ops.linear_simt(x[r:r + 1], w)[0], whole[r])
+
+
+class PagedCase:
+    """Sequences laid into a paged cache through shuffled pages."""
+
+    def __init__(self, dtype, lens, H, Hkv, dh, page_tokens=64, seed=0, n_slots=6):
+        g = torch.Generator().manual_seed(seed)
+        self.dtype, self.lens, self.H, self.Hkv, self.dh, self.pt = dtype, lens, H, Hkv, dh, page_tokens
+        max_pages = max(-(-n // page_tokens) for n in lens) + 1
+        n_pages = sum(-(-n // page_tokens) for n in lens) + 3
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        self.table = torch.full((n_slots, max_pages), -1, dtype=torch.int32)
+        self.slots = torch.randperm(n_slots, generator=g)[:len(lens)].tolist()
+        for s, n in zip(self.slots, lens):
+            for i in range(-(-n // page_tokens)):
+                self.table[s, i] = perm.pop()
+        self.k_cache = torch.full((n_pages, Hkv, page_tokens, dh), float("nan"), dtype=DT[dtype]).cuda()
+        self.v_cache = torch.full((n_pages, Hkv, page_tokens, dh), float("nan"), dtype=DT[dtype]).cuda()
+        self.q = [torch.randn(n, H, dh, generator=g).to(DT[dtype]) for n in lens]
+        self.k = [torch.randn(n, Hkv, dh, generator=g).to(DT[dtype]) for n in lens]
+        self.v = [torch.randn(n, Hkv, dh, generator=g).to(DT[dtype]) for n in lens]
+        self.status = torch.zeros(1, dtype=torch.int32).cuda()
+
+    def packed(self, ranges):
+        """Rows of the given (sequence, start, stop) ranges as one packed batch."""
+        qs, ks, vs, slot, pos = [], [], [], [], []
+        for i, a, b in ranges:
+            qs.append(self.q[i][a:b]); ks.append(self.k[i][a:b]); vs.append(self.v[i][a:b])
+            slot += [self.slots[i]] * (b - a)
+            pos += list(range(a, b))
+        cat = lambda xs, h: torch.cat(xs).reshape(-1, h * self.dh).contiguous().cuda()
+        return (cat(qs, self.H), cat(ks, self.Hkv), cat(vs, self.Hkv),
+                torch.tensor(slot, dtype=torch.int32).cuda(), torch.tensor(pos, dtype=torch.int32).cuda())
+
+
+def rope_table(max_pos, R, base=10000.0):
+    i = torch.arange(0, R, 2, dtype=torch.float64)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(base, dtype=torch.float64), -i / R)[None]
+    return torch.stack([ang.cos(), ang.sin()], -1).float().contiguous().cuda()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,Hkv,dh,R,window", [(4, 4, 16, 8, 0), (6, 2, 48, 48, 0), (2, 1, 80, 64, 0),
+                                                (3, 3, 256, 64, 0), (4, 2, 32, 16, 37), (2, 2, 16, 0, 64)])
+def test_rope_store_and_attention(dtype, H, Hkv, dh, R, window):
+    """Prompts in one packed step, then some tokens one by one, through shuffled pages;
+    compared with the plain rotary + causal attention on whole sequences."""
+    lens = [1, 70, 130, 64]
+    case = PagedCase(dtype, lens, H, Hkv, dh, seed=H * dh)
+    table = rope_table(256, R) if R else None
+    table_dev = case.table.cuda()
+    outs = [[] for _ in lens]
+
+    def run(ranges):
+        q, k, v, slot, pos = case.packed(ranges)
+        ops.rope_store(q, k, v, H, Hkv, dh, R, table, slot, pos, table_dev, case.pt, case.k_cache, case.v_cache, case.status)
+        o = ops.attention(q, H, Hkv, dh, dh ** -0.5, window, slot, pos, table_dev, case.pt, case.k_cache, case.v_cache, case.status)
+        row = 0
+        for i, a, b in ranges:
+            outs[i].append(o[row:row + b - a].cpu())
+            row += b - a
+
+    heads = [max(1, n - 5) for n in lens]
+    run([(i, 0, h) for i, h in enumerate(heads)])
+    for step in range(5):
+        rs = [(i, h + step, h + step + 1) for i, h in enumerate(heads) if h + step < lens[i]]
+        if rs:
+            run(rs)
+    assert int(case.status.item()) == 0
+    for i, n in enumerate(lens):
+        pos = np.arange(n)
+        q = P.rotary_interleaved(f64(case.q[i]), pos, R) if R else f64(case.q[i])
+        k = P.rotary_interleaved(f64(case.k[i]), pos, R) if R else f64(case.k[i])
+        if dtype == "bfloat16":     # the engine keeps rotated q and k in bfloat16
+            q = f64(torch.from_numpy(q).to(torch.bfloat16))
+            k = f64(torch.from_numpy(k).to(torch.bfloat16))
+        ref = P.causal_attention(q, k, f64(case.v[i]), window)
+        np.testing.assert_allclose(f64(torch.cat(outs[i])), ref, **tol(dtype), err_msg=f"sequence {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key(dtype):
+    """One key among hundreds matches the query: the output must be that key's value,
+    wherever it lies (first position, a page's edge, the window's edge)."""
+    H, dh, n = 2, 32, 300
+    for far, window in ((0, 0), (63, 0), (64, 0), (299, 0), (200, 100), (201, 100)):
+        case = PagedCase(dtype, [n], H, H, dh, seed=far)
+        case.q[0][:] = 0
+        case.k[0][:] = 0
+        case.q[0][n - 1, :, 0] = 12.0
+        case.k[0][far, :, 0] = 12.0
+        q, k, v, slot, pos = case.packed([(0, 0, n)])
+        tdev = case.table.cuda()
+        ops.rope_store(q, k, v, H, H, dh, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+        o = ops.attention(q, H, H, dh, dh ** -0.5, window, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+        got = f64(o[n - 1]).reshape(H, dh)
+        visible = window == 0 or far > n - 1 - window
+        if visible:
+            np.testing.assert_allclose(got, f64(case.v[0][far]), atol=5e-2 if dtype == "bfloat16" else 1e-4)
+        else:
+            lo = n - window
+            np.testing.assert_allclose(got, f64(case.v[0][lo:n]).mean(0), atol=5e-2 if dtype == "bfloat16" else 1e-4)
+
+
+def test_attention_skips_padding():
+    case = PagedCase("float32", [10], 2, 2, 16)
+    q, k, v, slot, pos = case.packed([(0, 0, 10)])
+    slot[3] = -1
+    tdev = case.table.cuda()
+    before = case.k_cache.clone()
+    ops.rope_store(q, k, v, 2, 2, 16, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+    page = int(case.table[case.slots[0], 0])
+    assert torch.isnan(case.k_cache[page, :, 3]).all() and not torch.isnan(case.k_cache[page, :, 2]).any()
+    o = ops.attention(q, 2, 2, 16, 0.25, 0, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+    assert torch.equal(o[3], torch.zeros_like(o[3]))
+    assert before.shape == case.k_cache.shape
+
+
+def test_argmax_lowest_index_wins_ties():
+    x = torch.full((4, 5000), -1.0)
+    x[0, 4999] = 3.0
+    x[1, 77] = 2.0; x[1, 4000] = 2.0
+    x[2] = 0.5
+    x[3, 1023] = 9.0; x[3, 1024] = 9.0
+    assert ops.argmax(x.cuda()).tolist() == [4999, 77, 0, 1023]
+    y = torch.randn(9, 321, generator=torch.Generator().manual_seed(1))
+    assert ops.argmax(y.cuda()).tolist() == [P.argmax_lowest(r.numpy()) for r in y]
+
+
+def test_repeat_penalty():
+    x = torch.tensor([[1.0, -2.0, 3.0, 0.5], [4.0, 4.0, -1.0, 2.0]])
+    recent = torch.zeros((2, 64), dtype=torch.int32)
+    recent[0, :3] = torch.tensor([0, 1, 0])
+    recent[1, :1] = torch.tensor([3])
+    count = torch.tensor([3, 1], dtype=torch.int32)
+    d = x.cuda()
+    ops.repeat_penalty(d, recent.cuda(), count.cuda(), 2.0)
+    ref0 = P.apply_repeat_penalty(x[0].double().numpy(), [0, 1, 0], 2.0)
+    ref1 = P.apply_repeat_penalty(x[1].double().numpy(), [3], 2.0)
+    np.testing.assert_allclose(d.cpu().numpy(), np.stack([ref0, ref1]), rtol=1e-6)
+
+
+@pytest.mark.parametrize("V", [320, 50400])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 0, 1.0), (0.7, 40, 0.9), (1.3, 5, 1.0),
+                                                     (0.9, 0, 0.5), (0.5, 1, 1.0)])
+def test_sample_against_plain(V, temperature, top_k, top_p):
+    """The chosen token's CDF interval in the plain pipeline must contain the draw (a
+    little widened: 32-bit sums in another order)."""
+    g = torch.Generator().manual_seed(V + top_k)
+    rows = 24
+    logits = (torch.randn(rows, V, generator=g) * 2.5).float()
+    draws = torch.rand(rows, generator=g).float()
+    draws[0], draws[1] = 0.0, 0.99999994
+    got = ops.sample(logits.cuda(), temperature, top_k, top_p, draws.cuda()).tolist()
+    for r in range(rows):
+        y = logits[r].double().numpy()
+        if temperature != 1.0:
+            y = logits[r].numpy().astype(np.float32) * np.float32(1.0 / temperature)
+            y = y.astype(np.float64)
+        if 0 < top_k < V:
+            y = P.top_k_filter(y, top_k)
+        if 0 < top_p < 1:
+            y = P.top_p_filter(y, top_p)
+        probs = P.softmax(y)
+        assert probs[got[r]] > 0, f"row {r}: token {got[r]} was filtered out"
+        lo, hi = P.cdf_interval(probs, got[r])
+        assert lo - 1e-4 <= float(draws[r]) <= hi + 1e-4, (r, got[r], lo, hi, float(draws[r]))
+
+
+def test_sample_top_p_ties_keep_lower_indices():
+    x = torch.zeros(1, 8)                       # eight equal tokens, p = 0.3 keeps the first three
+    got = set()
+    for r in np.linspace(0.0, 0.999, 40):
+        got.add(ops.sample(x.cuda(), 1.0, 0, 0.3, torch.tensor([r], dtype=torch.float32).cuda()).item())
+    assert got == {0, 1, 2}
