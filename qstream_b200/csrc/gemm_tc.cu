@@ -1,0 +1,267 @@
+// C = act(A W^T + bias) + res1 + res2 for bfloat16 A [M, K] and W [N, K] on the 5th-generation
+// tensor cores: TMA brings 128-byte-swizzled K-major tiles into a ring of shared-memory
+// stages, one elected thread issues tcgen05.mma (kind::f16, float32 accumulator in TMEM),
+// four warps read the accumulator back with tcgen05.ld and apply the epilogue in 32-bit.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA issuer,
+// warps 2..5 = epilogue (warp w reads TMEM lanes 32 * (w % 4) .. +31).
+//
+// Two operand arrangements of the same kernel:
+//   rows of A on the MMA's M side (128 per tile), rows of W on its N side (BN per tile): many tokens;
+//   SWAP: rows of W on the M side, the few tokens of a decode step on the N side (BN = 16..64),
+//         so no tensor-core row is spent on padding and every CTA streams its own slab of W.
+// Each output element is accumulated over K in one TMEM cell in ascending k, so a row's result
+// does not depend on the other rows of the batch.
+//
+// Sizes: any M, N; K a multiple of 8 (TMA row pitch of 16 bytes); tails are zero-filled by TMA.
+#include "common.cuh"
+#include "sm100.cuh"
+
+#include <mutex>
+#include <unordered_map>
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;             // rows of the M-side operand per tile = TMEM lanes
+constexpr int BK = 64;              // 64 bfloat16 = one 128-byte swizzled row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+struct Epilogue {
+    void* C; int c_dtype; long long ldc;
+    const void* bias; int bias_dtype; int act;
+    const __nv_bfloat16* res1; const __nv_bfloat16* res2; long long ldr;
+    int M, N;                       // tokens, output features
+};
+
+template <int BN> constexpr int stage_bytes() { return BM * BK * 2 + BN * BK * 2; }
+template <int BN> constexpr int num_stages() {
+    return SMEM_BUDGET / stage_bytes<BN>() > 12 ? 12 : SMEM_BUDGET / stage_bytes<BN>();
+}
+template <int BN> constexpr int smem_bytes() { return num_stages<BN>() * stage_bytes<BN>() + 1024 + 256; }
+
+__device__ __forceinline__ void store_out(const Epilogue& ep, int m, int n, float v) {
+    if (ep.bias) v += load_as_f32(ep.bias, ep.bias_dtype, n);
+    v = apply_activation(v, ep.act);
+    if (ep.res1) v += __bfloat162float(ep.res1[(size_t)m * ep.ldr + n]);
+    if (ep.res2) v += __bfloat162float(ep.res2[(size_t)m * ep.ldr + n]);
+    store_from_f32(ep.C, ep.c_dtype, (size_t)m * ep.ldc + n, v);
+}
+
+template <int BN, bool SWAP>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+               const Epilogue ep, const int K, int32_t* __restrict__ status) {
+    constexpr int STAGES = num_stages<BN>();
+    constexpr int STAGE = stage_bytes<BN>();
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr int CH = BN < 32 ? 16 : 32;             // accumulator columns read per tcgen05.ld
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    volatile uint32_t* aborted = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p0 = blockIdx.x * BM;                   // first row of the M-side operand
+    const int q0 = blockIdx.y * BN;                   // first row of the N-side operand
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *aborted = 0;
+        mbar_fence_init();
+        prefetch_tensormap(&map_p);
+        prefetch_tensormap(&map_q);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t phase = (kb / STAGES) & 1;
+                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 101); *aborted = 1; break; }
+                uint8_t* tile = smem + s * STAGE;
+                mbar_expect_tx(&full[s], STAGE);
+                tma_load_2d(tile, &map_p, &full[s], kb * BK, p0);
+                tma_load_2d(tile + BM * BK * 2, &map_q, &full[s], kb * BK, q0);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t phase = (kb / STAGES) & 1;
+                if (!mbar_wait(&full[s], phase)) { atomicExch(status, 102); *aborted = 1; ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t a_addr = smem_u32(smem + s * STAGE);
+                const uint64_t da = smem_desc_sw128(a_addr);
+                const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 elements of K = 32 bytes = 2 units of the descriptor's address field
+                    mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                }
+                mma_commit(&empty[s]);                // the stage is free once these MMAs have read it
+            }
+            mma_commit(acc_ready);                    // arrives even after a failed wait, so nobody hangs on it
+        }
+    } else {
+        const int quad = warp & 3;
+        bool ok = mbar_wait(acc_ready, 0);
+        if (!ok) atomicExch(status, 103);
+        ok = ok && *aborted == 0;
+        tc_fence_after_sync();
+        const int p = p0 + quad * 32 + lane;          // this thread's row of the M-side operand
+        if (ok) {
+#pragma unroll 1
+            for (int c = 0; c < BN / CH; ++c) {
+                uint32_t r[CH];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * CH);
+                if constexpr (CH == 32) tmem_load_32x32(taddr, r); else tmem_load_32x16(taddr, r);
+                tmem_load_wait();
+                if constexpr (!SWAP) {
+                    if (p < ep.M) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) {
+                            const int n = q0 + c * CH + j;
+                            if (n < ep.N) store_out(ep, p, n, __uint_as_float(r[j]));
+                        }
+                    }
+                } else {
+                    if (p < ep.N) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) {
+                            const int m = q0 + c * CH + j;
+                            if (m < ep.M) store_out(ep, m, p, __uint_as_float(r[j]));
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ----------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr);
+        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) h = h * 1000003u ^ (size_t)v;
+        return h;
+    }
+};
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] with row stride ld (elements): boxes of
+// box_rows x 64 elements, 128-byte swizzle, zero fill outside.  Maps are cached by their key.
+int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return QS_OK; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return qs_fail(QS_ERR_INTERNAL, "gemm_tc: the driver offers no cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return qs_fail(QS_ERR_INTERNAL, "gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%lld cols=%lld ld=%lld)",
+                       (int)r, rows, cols, ld);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return QS_OK;
+}
+
+template <int BN, bool SWAP>
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Epilogue& ep, int p_rows, int q_rows, int K,
+           int32_t* status, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             smem_bytes<BN>());
+        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc: shared memory of %d bytes refused: %s",
+                                             smem_bytes<BN>(), cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((p_rows + BM - 1) / BM, (q_rows + BN - 1) / BN);
+    gemm_tc_kernel<BN, SWAP><<<grid, THREADS, smem_bytes<BN>(), stream>>>(mp, mq, ep, K, status);
+    return qs_check_launch("gemm_tc");
+}
+
+}  // namespace
+
+// A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16 contiguous; C: [M, N] bfloat16 or float32.
+// res1/res2: bfloat16 [M, N] with row stride ldr, or null.  status: device int32 that receives a
+// non-zero code if a bounded wait inside the kernel ran out.
+QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const void* bias, int bias_dtype, int act,
+                      const void* res1, const void* res2, int M, int N, int K, long long lda, long long ldc,
+                      long long ldr, int32_t* status, cudaStream_t stream) {
+    if (M == 0 || N == 0) return QS_OK;
+    QS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+    QS_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc: K=%d and the row stride %lld must be multiples of 8", K, lda);
+    QS_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm_tc: operands must be 16-byte aligned");
+    QS_REQUIRE(c_dtype == QS_F32 || c_dtype == QS_BF16, "gemm_tc: unknown output type %d", c_dtype);
+    Epilogue ep{C, c_dtype, ldc, bias, bias_dtype, act, (const __nv_bfloat16*)res1, (const __nv_bfloat16*)res2, ldr, M, N};
+    CUtensorMap ma, mw;
+    int rc;
+    if (M > 64) {
+        QS_REQUIRE((M + BM - 1) / BM <= 65535 * 1 && (N + 127) / 128 <= 65535, "gemm_tc: sizes exceed the grid");
+        if ((rc = tensor_map(&ma, A, M, K, lda, BM)) != QS_OK) return rc;
+        if ((rc = tensor_map(&mw, W, N, K, K, 128)) != QS_OK) return rc;
+        return launch<128, false>(ma, mw, ep, M, N, K, status, stream);
+    }
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    if ((rc = tensor_map(&mw, W, N, K, K, BM)) != QS_OK) return rc;
+    if ((rc = tensor_map(&ma, A, M, K, lda, bn)) != QS_OK) return rc;
+    if (bn == 16) return launch<16, true>(mw, ma, ep, N, M, K, status, stream);
+    if (bn == 32) return launch<32, true>(mw, ma, ep, N, M, K, status, stream);
+    return launch<64, true>(mw, ma, ep, N, M, K, status, stream);
+}

@@ -1,7 +1,67 @@
 """The tensor-core matrix product (tcgen05 + TMA) for bfloat16 operands."""
 from __future__ import annotations
 
+from ctypes import c_int, c_longlong, c_void_p
+
+import torch
+
+from ..errors import QsError, QStreamError
+from . import ops
+
+_fn = None
+_status = {}
+
+
+def _entry():
+    global _fn
+    if _fn is None:
+        _fn = ops.bind("qs_gemm_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                      c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                                      c_void_p, c_void_p])
+    return _fn
+
+
+def status_word(device) -> torch.Tensor:
+    """A device int32 that the kernel sets if one of its bounded waits runs out."""
+    key = (device.type, device.index)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    code = int(status_word(torch.device(device)).item())
+    if code:
+        status_word(torch.device(device)).zero_()
+        raise QStreamError(QsError.INTERNAL, f"tensor-core matrix product: a wait inside the kernel ran out (code {code})")
+
 
 def takes(x, weight) -> bool:
-    """Whether the tensor-core kernel takes these operands."""
-    return False
+    """Whether the tensor-core kernel takes these operands: bfloat16, rows of 16-byte pitch."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+            and weight.is_contiguous() and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None) -> torch.Tensor:
+    M, K = x.shape
+    N, K2 = weight.shape
+    if K2 != K:
+        raise QStreamError(QsError.INVALID_INPUT, f"linear: x is [{M}, {K}] but weight is {tuple(weight.shape)}")
+    out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
+    res = [r for r in residuals if r is not None]
+    if len(res) > 2:
+        raise QStreamError(QsError.INVALID_INPUT, "linear: at most two residuals")
+    ldr = N
+    for r in res:
+        if r.shape != (M, N) or r.dtype != torch.bfloat16 or r.stride(1) != 1:
+            raise QStreamError(QsError.INVALID_INPUT, "linear: residual differs in shape or type")
+        ldr = r.stride(0)
+    if len(res) == 2 and res[0].stride(0) != res[1].stride(0):
+        raise QStreamError(QsError.INVALID_INPUT, "linear: residuals of two layouts")
+    res += [None, None]
+    ops.check(_entry()(ops.ptr(out), ops.dtype_code(out), ops.ptr(x), ops.ptr(weight), ops.ptr(bias),
+                       ops.dtype_code(bias) if bias is not None else 0, ops.ACTIVATIONS[activation],
+                       ops.ptr(res[0]), ops.ptr(res[1]), M, N, K, x.stride(0), N, ldr,
+                       ops.ptr(status_word(x.device)), ops.stream()))
+    return out

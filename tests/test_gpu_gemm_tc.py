@@ -1,0 +1,71 @@
+"""The tensor-core matrix product alone, against float64, at many shapes."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gptj as P
+from qstream_b200.csrc import gemm_tc
+
+pytestmark = pytest.mark.gpu
+
+
+def f64(t):
+    return t.detach().cpu().to(torch.float64).numpy()
+
+
+SHAPES = [(1, 128, 64), (1, 4096, 4096), (3, 200, 96), (8, 320, 320), (16, 64, 256), (17, 136, 72),
+          (33, 500, 1024), (64, 256, 64), (65, 256, 64), (128, 128, 128), (200, 330, 520), (256, 384, 2048),
+          (1000, 96, 320), (2048, 512, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_plain_product(M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
+    assert gemm_tc.takes(x, w)
+    got = gemm_tc.linear(x, w, out_dtype=torch.float32)
+    gemm_tc.check_status(x.device)
+    ref = f64(x) @ f64(w).T
+    np.testing.assert_allclose(f64(got), ref, atol=2e-3, rtol=2e-3)   # float32 accumulation of exact products
+
+
+@pytest.mark.parametrize("M", [5, 40, 300])
+@pytest.mark.parametrize("act", [None, "gelu_new", "gelu"])
+def test_epilogue(M, act):
+    N, K = 264, 136
+    g = torch.Generator().manual_seed(M)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
+    bias = torch.randn(N, generator=g).bfloat16().cuda()
+    r1 = torch.randn(M, N, generator=g).bfloat16().cuda()
+    r2 = torch.randn(M, N, generator=g).bfloat16().cuda()
+    fn = {None: lambda u: u, "gelu_new": P.gelu_new, "gelu": P.gelu_erf}[act]
+    ref = fn(f64(x) @ f64(w).T + f64(bias)) + f64(r1) + f64(r2)
+    got32 = gemm_tc.linear(x, w, bias, act, (r1, r2), torch.float32)
+    np.testing.assert_allclose(f64(got32), ref, atol=3e-3, rtol=3e-3)
+    got16 = gemm_tc.linear(x, w, bias, act, (r1, r2))
+    assert got16.dtype == torch.bfloat16
+    np.testing.assert_allclose(f64(got16), ref, atol=3e-2, rtol=1e-2)
+    fbias = bias.float()
+    got = gemm_tc.linear(x, w, fbias, act, (), torch.float32)
+    np.testing.assert_allclose(f64(got), fn(f64(x) @ f64(w).T + f64(bias)), atol=3e-3, rtol=3e-3)
+    gemm_tc.check_status(x.device)
+
+
+def test_strided_input_and_row_independence():
+    g = torch.Generator().manual_seed(3)
+    buf = torch.randn(90, 3 * 128, generator=g).bfloat16().cuda()
+    x = buf[:, 128:256]                                   # a column slice: row stride 384
+    w = (torch.randn(200, 128, generator=g) / 11).bfloat16().cuda()
+    assert gemm_tc.takes(x, w)
+    whole = gemm_tc.linear(x, w, out_dtype=torch.float32)
+    np.testing.assert_allclose(f64(whole), f64(x) @ f64(w).T, atol=2e-3, rtol=2e-3)
+    # one row's result is the same bits in a batch of 90 (tokens on the M side) and of 2, 20, 50
+    # (tokens on the N side): one TMEM cell per element, products summed in ascending k
+    for rows in (slice(7, 9), slice(10, 30), slice(40, 90)):
+        part = gemm_tc.linear(x[rows], w, out_dtype=torch.float32)
+        assert torch.equal(part, whole[rows])
+    gemm_tc.check_status(x.device)
