@@ -75,7 +75,22 @@ def bind(name: str, argtypes, restype=c_int):
     return fn
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of the library have been launched (replayed graph nodes included)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
 def check(rc: int) -> None:
+    global _launches
+    _launches += 1
     if rc != 0:
         detail = library().qs_last_error().decode(errors="replace")
         try:

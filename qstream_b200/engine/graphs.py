@@ -1,0 +1,99 @@
+"""Decode steps as CUDA graphs.
+
+A decode step (one token per sequence) launches a few hundred small kernels; captured
+once per batch-size bucket and replayed, the launches cost the host almost nothing.  The
+graph reads the step's metadata (tokens, slots, positions) from fixed device buffers that
+are refreshed by one copy from pinned memory before each replay; rows beyond the live
+sequences carry slot -1 and are skipped by every kernel that touches the cache.  Logits
+of all rows land in a fixed buffer.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .step import StepBatch, StepContext
+
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+_RING = 4
+
+
+def bucket_for(n: int) -> int:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    return -(-n // 64) * 64
+
+
+class DecodeGraph:
+    """One captured decode step for `rows` packed rows."""
+
+    def __init__(self, engine, rows: int):
+        self.engine = engine
+        self.rows = rows
+        dev = engine.device
+        sizes = [rows, rows, rows, rows, rows, rows + 1, rows]
+        self.offs = np.concatenate([[0], np.cumsum(sizes)]).astype(int)
+        n = int(self.offs[-1])
+        self.meta = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.staging = [torch.zeros(n, dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.staging_np = [s.numpy() for s in self.staging]
+        self.events = [None] * _RING
+        self.turn = 0
+        v = [self.meta[self.offs[i]:self.offs[i + 1]] for i in range(7)]
+        # fixed parts of the metadata: every row is wanted, row i is sequence i
+        for s in self.staging_np:
+            s[self.offs[1]:self.offs[2]] = -1
+            s[self.offs[3]:self.offs[4]] = np.arange(rows)
+            s[self.offs[5]:self.offs[6]] = np.arange(rows + 1)
+        self.meta.copy_(self.staging[0])
+        self.batch = StepBatch(n_seq=rows, n_tokens=rows, n_want=rows, tokens=v[0], tok_slot=v[1], tok_pos=v[2],
+                               want_rows=v[3], seq_slot=v[4], seq_start=v[5], seq_p0=v[6],
+                               slots=[], new_tokens=[1] * rows, p0=[], decode=True, max_new=1, max_total=0)
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+    def capture(self) -> None:
+        from ..csrc import ops
+        eng = self.engine
+        ctx = StepContext(self.batch, eng.cache, eng.status)
+        stream = torch.cuda.Stream(device=eng.device)
+        stream.wait_stream(torch.cuda.current_stream(eng.device))
+        with torch.cuda.stream(stream):
+            eng.model.forward(ctx)                      # warm-up: first-call set-up happens outside the capture
+        torch.cuda.current_stream(eng.device).wait_stream(stream)
+        torch.cuda.synchronize(eng.device)
+        self.graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(self.graph):
+            self.logits = eng.model.forward(ctx)
+        self.launches = ops.launch_count() - before
+
+    def run(self, slots, tokens, p0) -> torch.Tensor:
+        """Refresh the metadata and replay; returns the logits buffer [rows, vocab]."""
+        i = self.turn
+        self.turn = (self.turn + 1) % _RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()                # the copy that last read this buffer is done
+        s, o, n = self.staging_np[i], self.offs, len(slots)
+        s[o[0]:o[0] + n] = tokens
+        s[o[0] + n:o[1]] = 0
+        s[o[1]:o[1] + n] = slots
+        s[o[1] + n:o[2]] = -1
+        s[o[2]:o[2] + n] = p0
+        s[o[2] + n:o[3]] = 0
+        s[o[4]:o[4] + n] = slots
+        s[o[4] + n:o[5]] = -1
+        s[o[6]:o[6] + n] = p0
+        s[o[6] + n:o[7]] = 0
+        self.meta.copy_(self.staging[i], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        if self.graph is None:
+            self.capture()
+        self.graph.replay()
+        from ..csrc import ops
+        ops.count_launches(self.launches)
+        return self.logits

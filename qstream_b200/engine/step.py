@@ -78,7 +78,7 @@ class Engine:
     """
 
     def __init__(self, model: CausalLM, max_tokens: Optional[int] = None, max_batch: int = 64,
-                 max_context: Optional[int] = None, verbose: int = 0):
+                 max_context: Optional[int] = None, verbose: int = 0, use_graphs: bool = True):
         self.model = model
         self.device = model.runtime.device
         self.dtype = model.runtime.dtype
@@ -91,6 +91,8 @@ class Engine:
         self._check_budget(kv_needs, max_tokens)
         self.cache = SequenceCache(kv_needs, state_needs, max_tokens, max_batch, ctx, self.dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self._graphs = {}
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else None
         if verbose:
             import sys
@@ -184,12 +186,47 @@ class Engine:
         """Run one step.  `want[i]` lists the places among sequence i's new tokens whose
         logits are asked for (default: the last).  Returns float32 logits [n_want, vocab]
         on the device, in the order of the sequences and of `want`; None if none is wanted."""
+        if self.use_graphs and tokens and all(len(t) == 1 for t in tokens):
+            return self._decode_step(slots, tokens, want)
         batch = self.build_batch(slots, tokens, want)
         if batch.n_tokens == 0:
             return None
         logits = self.model.forward(StepContext(batch, self.cache, self.status))
         self.cache.commit(batch.slots, batch.new_tokens)
         return logits
+
+    def _decode_step(self, slots, tokens, want):
+        """One token per sequence: replay the captured graph of the batch's size bucket."""
+        from ..csrc import ops
+        from .graphs import DecodeGraph, bucket_for
+        n = len(slots)
+        if len(tokens) != n or (want is not None and len(want) != n):
+            raise QStreamError(QsError.INVALID_INPUT, "step: slots, tokens and want differ in length")
+        V = self.model.vocab_size
+        toks = [int(t[0]) for t in tokens]
+        for s, tok in zip(slots, toks):
+            if not 0 <= tok < V:
+                raise QStreamError(QsError.INVALID_INPUT, f"token id {tok} (slot {s}) outside the vocabulary of {V}")
+        if want is not None:
+            for w in want:
+                if any(p != 0 for p in w):
+                    raise QStreamError(QsError.INVALID_INPUT, f"wanted place {w} outside the 1 token given")
+        ones = [1] * n
+        self.cache.prepare(slots, ones)
+        p0 = [self.cache.length(s) for s in slots]
+        rows = bucket_for(n)
+        graph = self._graphs.get(rows)
+        if graph is None:
+            graph = self._graphs[rows] = DecodeGraph(self, rows)
+        logits = graph.run(slots, toks, p0)
+        self.cache.commit(slots, ones)
+        if want is None or all(len(w) == 1 for w in want):
+            return logits[:n]
+        picked = [i for i, w in enumerate(want) for _ in w]
+        if not picked:
+            return None
+        idx = torch.tensor(picked, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        return ops.gather_rows(logits, idx)
 
     def check_status(self) -> None:
         """Raise if a kernel reported a fault (this waits for the device)."""
