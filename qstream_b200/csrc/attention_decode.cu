@@ -1,0 +1,253 @@
+// Decode attention for bfloat16: one query token per sequence against its paged cache, with the
+// keys cut into splits of 256 (four pages of 64) that run as separate CTAs, and a merge kernel.
+//
+// The kernel is bound by the bytes of K and V it streams (one multiply-add per byte and head),
+// so it runs on the CUDA cores with 16-byte loads; scores, maxima, exponentials, sums and the
+// output accumulator are 32-bit.  A split's boundaries depend only on absolute key positions
+// and the merge adds the splits in ascending order, so a sequence's result depends on its own
+// length only, not on the batch or on where its pages lie.
+//
+//   s[u] = q.k[u] / sqrt(dh) over keys first <= u <= pos     (QStream src/engine.c:888-906)
+//   softmax with max subtraction                             (src/kernels_scalar.c:188-213)
+//   o = sum_u a[u] v[u]                                      (src/engine.c:913-922)
+#include "common.cuh"
+
+namespace {
+
+constexpr int PAGE = 64;
+constexpr int WARPS = 4;
+constexpr int SPLIT = PAGE * WARPS;          // keys per CTA
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float (&f)[8]) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// Lanes are grouped GS to a key (GS = the power of two >= dh / 8, at most 32); lane `c` of a group
+// owns the 16-byte chunks c, c + GS, ... (NCH of them) of the head.  KPL = 32 / GS keys are
+// handled per warp instruction.
+template <int NCH>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict__ q, size_t ldq,
+                    const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                    const int32_t* __restrict__ page_table, int max_pages,
+                    const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                    int n_heads, int n_kv_heads, int dh, int gs_log2, float scale, int window, int max_splits,
+                    int32_t* __restrict__ status) {
+    __shared__ float s_scores[WARPS][PAGE];
+    __shared__ float s_m[WARPS], s_l[WARPS];
+    extern __shared__ float s_acc[];                 // [WARPS][dh]
+
+    const int split = blockIdx.x, head = blockIdx.y, t = blockIdx.z;
+    const int slot = tok_slot[t];
+    if (slot < 0) return;
+    const int pos = tok_pos[t];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    if (split * SPLIT > pos || (split + 1) * SPLIT <= first) return;       // no visible key in this split
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int GS = 1 << gs_log2, KPL = 32 >> gs_log2;
+    const int chunk = lane & (GS - 1), sub = lane >> gs_log2;
+    const int n_chunks = dh >> 3;
+    const int kvh = head / (n_heads / n_kv_heads);
+
+    // this lane's part of the query, in 32-bit
+    float qf[NCH][8];
+    const __nv_bfloat16* qrow = q + (size_t)t * ldq + (size_t)head * dh;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+        const int c = chunk + i * GS;
+        if (c < n_chunks) bf16x8_to_f32(*reinterpret_cast<const uint4*>(qrow + c * 8), qf[i]);
+        else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) qf[i][j] = 0.f;
+        }
+    }
+
+    float acc[NCH][8];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    const int key0 = split * SPLIT + warp * PAGE;     // this warp's page of keys
+    if (key0 <= pos && key0 + PAGE > first) {
+        const int page = page_table[(size_t)slot * max_pages + (key0 >> 6)];
+        if (page < 0) {
+            if (lane == 0) atomicExch(status, 3);
+        } else {
+            const size_t base = ((size_t)page * n_kv_heads + kvh) * PAGE * dh;
+            const __nv_bfloat16* kp = k_cache + base;
+            const __nv_bfloat16* vp = v_cache + base;
+            const int n_keys = min(PAGE, pos - key0 + 1);
+            // scores of the page's keys
+            for (int it = 0; it * KPL < n_keys; ++it) {
+                const int kk = it * KPL + sub;
+                float dot = 0.f;
+                if (kk < n_keys) {
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        const int c = chunk + i * GS;
+                        if (c < n_chunks) {
+                            float kf[8];
+                            bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(kp + (size_t)kk * dh + c * 8)), kf);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) dot = fmaf(qf[i][j], kf[j], dot);
+                        }
+                    }
+                }
+                for (int o = GS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                if (chunk == 0 && kk < PAGE) s_scores[warp][kk] = (kk < n_keys && key0 + kk >= first) ? dot * scale : -INFINITY;
+            }
+            __syncwarp();
+            // softmax weights of the page: lane handles keys lane and lane + 32
+            float s0 = lane < n_keys ? s_scores[warp][lane] : -INFINITY;
+            float s1 = lane + 32 < n_keys ? s_scores[warp][lane + 32] : -INFINITY;
+            m = warp_max(fmaxf(s0, s1));
+            const float p0 = m == -INFINITY ? 0.f : expf(s0 - m);
+            const float p1 = m == -INFINITY ? 0.f : expf(s1 - m);
+            l = warp_sum(p0 + p1);
+            __syncwarp();
+            s_scores[warp][lane] = p0;
+            s_scores[warp][lane + 32] = p1;
+            __syncwarp();
+            // weighted values
+            for (int it = 0; it * KPL < n_keys; ++it) {
+                const int kk = it * KPL + sub;
+                if (kk < n_keys) {
+                    const float p = s_scores[warp][kk];
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        const int c = chunk + i * GS;
+                        if (c < n_chunks) {
+                            float vf[8];
+                            bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(vp + (size_t)kk * dh + c * 8)), vf);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(p, vf[j], acc[i][j]);
+                        }
+                    }
+                }
+            }
+            // add the KPL key groups of the warp (they hold different keys of the same dims)
+            for (int o = GS; o < 32; o <<= 1) {
+#pragma unroll
+                for (int i = 0; i < NCH; ++i)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[i][j] += __shfl_xor_sync(0xffffffffu, acc[i][j], o);
+            }
+        }
+    }
+
+    // merge the four warps in warp order
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+    if (sub == 0) {
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            const int c = chunk + i * GS;
+            if (c < n_chunks) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s_acc[(size_t)warp * dh + c * 8 + j] = acc[i][j];
+            }
+        }
+    }
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_m[w]);
+    float* out = partial + (((size_t)t * n_heads + head) * max_splits + split) * (dh + 2);
+    for (int d = threadIdx.x; d < dh; d += blockDim.x) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w)
+            if (s_m[w] != -INFINITY) o += s_acc[(size_t)w * dh + d] * expf(s_m[w] - M);
+        out[d] = o;
+    }
+    if (threadIdx.x == 0) {
+        float L = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w)
+            if (s_m[w] != -INFINITY) L += s_l[w] * expf(s_m[w] - M);
+        out[dh] = M;
+        out[dh + 1] = L;
+    }
+}
+
+// One block per (token, head): add the splits' partial results in ascending split order.
+__global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo, const float* __restrict__ partial,
+                                    const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                                    int n_heads, int dh, int window, int max_splits) {
+    const int head = blockIdx.x, t = blockIdx.y;
+    __nv_bfloat16* o = out + (size_t)t * ldo + (size_t)head * dh;
+    if (tok_slot[t] < 0) {
+        for (int d = threadIdx.x; d < dh; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int pos = tok_pos[t];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = first / SPLIT, s_hi = pos / SPLIT;
+    const float* base = partial + ((size_t)t * n_heads + head) * max_splits * (dh + 2);
+    float M = -INFINITY;
+    for (int s = s_lo; s <= s_hi; ++s) M = fmaxf(M, base[(size_t)s * (dh + 2) + dh]);
+    float L = 0.f;
+    for (int s = s_lo; s <= s_hi; ++s) {
+        const float ms = base[(size_t)s * (dh + 2) + dh];
+        if (ms != -INFINITY) L += base[(size_t)s * (dh + 2) + dh + 1] * expf(ms - M);
+    }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    for (int d = threadIdx.x; d < dh; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = s_lo; s <= s_hi; ++s) {
+            const float ms = base[(size_t)s * (dh + 2) + dh];
+            if (ms != -INFINITY) acc += base[(size_t)s * (dh + 2) + d] * expf(ms - M);
+        }
+        o[d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+}  // namespace
+
+// How many floats of scratch `qs_attention_decode` needs.
+QS_API long long qs_attention_decode_scratch(int T_tokens, int n_heads, int dh, int max_context) {
+    const long long max_splits = (max_context + SPLIT - 1) / SPLIT;
+    return (long long)T_tokens * n_heads * max_splits * (dh + 2);
+}
+
+// out [T, n_heads * dh] bfloat16.  One query token per row; `max_context` bounds every row's
+// position + 1 and fixes the grid, so the same launch serves every length (CUDA graphs).
+// `scratch`: float32, at least qs_attention_decode_scratch(...) elements; contents need no
+// initialisation.
+QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
+                               const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
+                               const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
+                               int n_kv_heads, int dh, float scale, int window, int max_context,
+                               float* scratch, int32_t* status, cudaStream_t stream) {
+    if (T_tokens == 0) return QS_OK;
+    QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && dh > 0 && max_context > 0, "attention_decode: bad sizes");
+    QS_REQUIRE(page_tokens == PAGE, "attention_decode: pages of %d tokens, the kernel is built for %d", page_tokens, PAGE);
+    QS_REQUIRE(n_heads % n_kv_heads == 0, "attention_decode: %d query heads are no multiple of %d key heads", n_heads, n_kv_heads);
+    QS_REQUIRE(dh % 8 == 0 && dh <= 512, "attention_decode: head size %d must be a multiple of 8, at most 512", dh);
+    QS_REQUIRE(ldq % 8 == 0 && ((uintptr_t)q % 16) == 0, "attention_decode: queries must be 16-byte aligned rows");
+    QS_REQUIRE(T_tokens <= 65535 && n_heads <= 65535, "attention_decode: sizes exceed the grid");
+    const int max_splits = (max_context + SPLIT - 1) / SPLIT;
+    const int n_chunks = dh / 8;
+    int gs_log2 = 0;
+    while ((1 << gs_log2) < n_chunks && gs_log2 < 5) ++gs_log2;
+    const int nch = (n_chunks + 31) / 32;
+    dim3 grid(max_splits, n_heads, T_tokens);
+    const size_t smem = (size_t)WARPS * dh * sizeof(float);
+#define GO(NCH) decode_split_kernel<NCH><<<grid, WARPS * 32, smem, stream>>>( \
+        scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
+        page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, max_splits, status)
+    if (nch == 1) GO(1); else GO(2);
+#undef GO
+    int rc = qs_check_launch("attention_decode");
+    if (rc != QS_OK) return rc;
+    decode_merge_kernel<<<dim3(n_heads, T_tokens), dh >= 128 ? 128 : 64, 0, stream>>>(
+        (__nv_bfloat16*)out, (size_t)ldo, scratch, tok_slot, tok_pos, n_heads, dh, window, max_splits);
+    return qs_check_launch("attention_decode merge");
+}

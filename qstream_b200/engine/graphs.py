@@ -9,6 +9,9 @@ of all rows land in a fixed buffer.
 """
 from __future__ import annotations
 
+import gc
+import weakref
+
 import numpy as np
 import torch
 
@@ -29,7 +32,7 @@ class DecodeGraph:
     """One captured decode step for `rows` packed rows."""
 
     def __init__(self, engine, rows: int):
-        self.engine = engine
+        self._engine = weakref.ref(engine)          # the engine owns its graphs, not the other way round
         self.rows = rows
         dev = engine.device
         sizes = [rows, rows, rows, rows, rows, rows + 1, rows]
@@ -56,7 +59,7 @@ class DecodeGraph:
 
     def capture(self) -> None:
         from ..csrc import ops
-        eng = self.engine
+        eng = self._engine()
         ctx = StepContext(self.batch, eng.cache, eng.status)
         stream = torch.cuda.Stream(device=eng.device)
         stream.wait_stream(torch.cuda.current_stream(eng.device))
@@ -66,8 +69,16 @@ class DecodeGraph:
         torch.cuda.synchronize(eng.device)
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(self.graph):
-            self.logits = eng.model.forward(ctx)
+        # A dead graph freed by the garbage collector in mid-capture would invalidate the capture.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = eng.model.forward(ctx)
+        finally:
+            if gc_was_on:
+                gc.enable()
         self.launches = ops.launch_count() - before
 
     def run(self, slots, tokens, p0) -> torch.Tensor:

@@ -254,3 +254,55 @@ def test_sample_top_p_ties_keep_lower_indices():
     for r in np.linspace(0.0, 0.999, 40):
         got.add(ops.sample(x.cuda(), 1.0, 0, 0.3, torch.tensor([r], dtype=torch.float32).cuda()).item())
     assert got == {0, 1, 2}
+
+
+@pytest.mark.parametrize("H,Hkv,dh,window", [(4, 4, 16, 0), (16, 16, 256, 0), (6, 2, 48, 0), (2, 1, 80, 0),
+                                             (4, 4, 64, 300), (3, 3, 128, 0), (2, 2, 320, 0), (2, 2, 32, 1)])
+def test_decode_attention_kernel(H, Hkv, dh, window):
+    """The split decode kernel (bfloat16) against the plain attention at many lengths: page and
+    split edges, one key, a window."""
+    from qstream_b200.csrc import attention_bf16
+    lens = [1, 64, 65, 256, 257, 700, 1024]
+    case = PagedCase("bfloat16", lens, H, Hkv, dh, seed=dh + window, n_slots=9)
+    tdev = case.table.cuda()
+    q, k, v, slot, pos = case.packed([(i, 0, n) for i, n in enumerate(lens)])
+    ops.rope_store(None, k, v, 0, Hkv, dh, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+    last_rows = np.cumsum(lens) - 1
+    ql = q[torch.as_tensor(last_rows).cuda()].contiguous()
+    slot_l = torch.tensor(case.slots[:len(lens)], dtype=torch.int32).cuda()
+    pos_l = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    # a padding row in the middle
+    slot_l = torch.cat([slot_l[:3], torch.tensor([-1], dtype=torch.int32).cuda(), slot_l[3:]])
+    pos_l = torch.cat([pos_l[:3], torch.tensor([0], dtype=torch.int32).cuda(), pos_l[3:]])
+    ql = torch.cat([ql[:3], ql[:1], ql[3:]])
+    got = attention_bf16.decode(ql, H, Hkv, dh, dh ** -0.5, window, slot_l, pos_l, tdev, case.pt,
+                                case.k_cache, case.v_cache, 1100, case.status)
+    gen = ops.attention(ql, H, Hkv, dh, dh ** -0.5, window, slot_l, pos_l, tdev, case.pt, case.k_cache,
+                        case.v_cache, case.status)
+    assert int(case.status.item()) == 0
+    assert torch.equal(got[3], torch.zeros_like(got[3]))
+    keep = [0, 1, 2, 4, 5, 6, 7]
+    for j, i in zip(keep, range(len(lens))):
+        ref = P.causal_attention(f64(case.q[i]), f64(case.k[i]), f64(case.v[i]), window)[-1]
+        np.testing.assert_allclose(f64(got[j]), ref, atol=2e-2, rtol=2e-2, err_msg=f"length {lens[i]}")
+        np.testing.assert_allclose(f64(got[j]), f64(gen[j]), atol=2e-2, rtol=2e-2)
+
+
+def test_decode_attention_does_not_depend_on_the_batch():
+    from qstream_b200.csrc import attention_bf16
+    H, dh = 4, 64
+    lens = [300, 900, 10]
+    case = PagedCase("bfloat16", lens, H, H, dh, seed=3)
+    tdev = case.table.cuda()
+    q, k, v, slot, pos = case.packed([(i, 0, n) for i, n in enumerate(lens)])
+    ops.rope_store(None, k, v, 0, H, dh, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+    rows = torch.as_tensor(np.cumsum(lens) - 1).cuda()
+    ql = q[rows].contiguous()
+    slot_l = torch.tensor(case.slots, dtype=torch.int32).cuda()
+    pos_l = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    args = (H, H, dh, dh ** -0.5, 0)
+    both = attention_bf16.decode(ql, *args, slot_l, pos_l, tdev, case.pt, case.k_cache, case.v_cache, 1024, case.status)
+    for i in range(3):
+        alone = attention_bf16.decode(ql[i:i + 1], *args, slot_l[i:i + 1], pos_l[i:i + 1], tdev, case.pt,
+                                      case.k_cache, case.v_cache, 2048, case.status)
+        assert torch.equal(alone[0], both[i])
