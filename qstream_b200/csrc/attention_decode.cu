@@ -251,3 +251,46 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
         (__nv_bfloat16*)out, (size_t)ldo, scratch, tok_slot, tok_pos, n_heads, dh, window, max_splits);
     return qs_check_launch("attention_decode merge");
 }
+
+// ----------------------------------------------------------------------------- no allocation
+//
+// The same decode attention for callers that cannot allocate device memory (see
+// qstream_no_alloc.h): the partial results of the key splits go to a fixed array in the
+// library instead of a buffer from the caller.
+#include "qstream_no_alloc.h"
+
+// In host code this name is only a handle for cudaGetSymbolAddress, not a device address.
+static __device__ __align__(256) float g_decode_static_scratch[QS_DECODE_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_decode_static_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+QS_API int qs_attention_decode_static(void* out, long long ldo, const void* q, long long ldq,
+                                      const void* k_cache, const void* v_cache,
+                                      const int32_t* page_table, int max_pages, int page_tokens,
+                                      const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens,
+                                      int n_heads, int n_kv_heads, int dh, float scale, int window,
+                                      int max_context, int32_t* status, cudaStream_t stream) {
+    if (T_tokens == 0) return QS_OK;
+    QS_REQUIRE(T_tokens > 0 && n_heads > 0 && dh > 0 && max_context > 0, "attention_decode_static: bad sizes");
+    const long long need = qs_attention_decode_scratch(T_tokens, n_heads, dh, max_context);
+    QS_REQUIRE(need <= (long long)QS_DECODE_STATIC_SCRATCH_FLOATS,
+               "attention_decode_static: the call needs %lld floats of scratch, the built-in array holds %d "
+               "(tokens * heads * ceil(context / 256) * (head size + 2))", need, QS_DECODE_STATIC_SCRATCH_FLOATS);
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    QS_REQUIRE(device >= 0 && device < kMaxDevices, "attention_decode_static: device %d out of range", device);
+    if (!g_decode_static_ptr[device]) {             // first call on this device: find the array's device address
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
+        if (e != cudaSuccess || !p)
+            return qs_fail(QS_ERR_INTERNAL, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_decode_static_ptr[device] = p;
+    }
+    return qs_attention_decode(out, ldo, q, ldq, k_cache, v_cache, page_table, max_pages, page_tokens, tok_slot,
+                               tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window, max_context,
+                               g_decode_static_ptr[device], status, stream);
+}
