@@ -83,6 +83,8 @@ class DecodeGraph:
 
     def run(self, slots, tokens, p0) -> torch.Tensor:
         """Refresh the metadata and replay; returns the logits buffer [rows, vocab]."""
+        if self.graph is None:
+            self.capture()          # while the metadata still holds padding only: the warm-up run touches no sequence
         i = self.turn
         self.turn = (self.turn + 1) % _RING
         if self.events[i] is not None:
@@ -102,8 +104,6 @@ class DecodeGraph:
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
-        if self.graph is None:
-            self.capture()
         self.graph.replay()
         from ..csrc import ops
         ops.count_launches(self.launches)
