@@ -17,6 +17,7 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int WARPS = 4;
 constexpr int SPLIT = PAGE * WARPS;          // keys per CTA
+constexpr int UNROLL = 8;                    // 16-byte loads in flight per lane
 
 __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float (&f)[8]) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -85,24 +86,33 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
             const __nv_bfloat16* kp = k_cache + base;
             const __nv_bfloat16* vp = v_cache + base;
             const int n_keys = min(PAGE, pos - key0 + 1);
-            // scores of the page's keys
-            for (int it = 0; it * KPL < n_keys; ++it) {
-                const int kk = it * KPL + sub;
-                float dot = 0.f;
-                if (kk < n_keys) {
+            // scores of the page's keys, UNROLL warp loads in flight at a time
+            for (int it0 = 0; it0 * KPL < n_keys; it0 += UNROLL) {
+                uint4 raw[UNROLL][NCH];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int kk = (it0 + u) * KPL + sub;
 #pragma unroll
                     for (int i = 0; i < NCH; ++i) {
                         const int c = chunk + i * GS;
-                        if (c < n_chunks) {
-                            float kf[8];
-                            bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(kp + (size_t)kk * dh + c * 8)), kf);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) dot = fmaf(qf[i][j], kf[j], dot);
-                        }
+                        raw[u][i] = (kk < n_keys && c < n_chunks)
+                            ? __ldg(reinterpret_cast<const uint4*>(kp + (size_t)kk * dh + c * 8)) : make_uint4(0, 0, 0, 0);
                     }
                 }
-                for (int o = GS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                if (chunk == 0 && kk < PAGE) s_scores[warp][kk] = (kk < n_keys && key0 + kk >= first) ? dot * scale : -INFINITY;
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int kk = (it0 + u) * KPL + sub;
+                    float dot = 0.f;
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        float kf[8];
+                        bf16x8_to_f32(raw[u][i], kf);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) dot = fmaf(qf[i][j], kf[j], dot);
+                    }
+                    for (int o = GS >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                    if (chunk == 0 && kk < PAGE) s_scores[warp][kk] = (kk < n_keys && key0 + kk >= first) ? dot * scale : -INFINITY;
+                }
             }
             __syncwarp();
             // softmax weights of the page: lane handles keys lane and lane + 32
@@ -117,19 +127,28 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
             s_scores[warp][lane + 32] = p1;
             __syncwarp();
             // weighted values
-            for (int it = 0; it * KPL < n_keys; ++it) {
-                const int kk = it * KPL + sub;
-                if (kk < n_keys) {
-                    const float p = s_scores[warp][kk];
+            for (int it0 = 0; it0 * KPL < n_keys; it0 += UNROLL) {
+                uint4 raw[UNROLL][NCH];
+                float pw[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u) {
+                    const int kk = (it0 + u) * KPL + sub;
+                    pw[u] = kk < n_keys ? s_scores[warp][kk] : 0.f;
 #pragma unroll
                     for (int i = 0; i < NCH; ++i) {
                         const int c = chunk + i * GS;
-                        if (c < n_chunks) {
-                            float vf[8];
-                            bf16x8_to_f32(__ldg(reinterpret_cast<const uint4*>(vp + (size_t)kk * dh + c * 8)), vf);
+                        raw[u][i] = (kk < n_keys && c < n_chunks)
+                            ? __ldg(reinterpret_cast<const uint4*>(vp + (size_t)kk * dh + c * 8)) : make_uint4(0, 0, 0, 0);
+                    }
+                }
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(p, vf[j], acc[i][j]);
-                        }
+                for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        float vf[8];
+                        bf16x8_to_f32(raw[u][i], vf);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(pw[u], vf[j], acc[i][j]);
                     }
                 }
             }

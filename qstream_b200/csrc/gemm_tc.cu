@@ -28,7 +28,10 @@ constexpr int BM = 128;             // rows of the M-side operand per tile = TME
 constexpr int BK = 64;              // 64 bfloat16 = one 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_BUDGET_BIG = 200 * 1024;     // many tokens: one CTA per SM, deep ring
+constexpr int SMEM_BUDGET_SWAP = 100 * 1024;    // few tokens: two CTAs per SM stream weights side by side
+constexpr int TARGET_CTAS = 2 * 148;            // CTAs resident at once in the weight-streaming arrangement
+constexpr int MIN_KB_PER_SPLIT = 8;             // k-blocks of 64 a split-K slice keeps at least
 
 struct Epilogue {
     void* C; int c_dtype; long long ldc;
@@ -38,10 +41,10 @@ struct Epilogue {
 };
 
 template <int BN> constexpr int stage_bytes() { return BM * BK * 2 + BN * BK * 2; }
-template <int BN> constexpr int num_stages() {
-    return SMEM_BUDGET / stage_bytes<BN>() > 12 ? 12 : SMEM_BUDGET / stage_bytes<BN>();
+template <int BN, bool SWAP> constexpr int num_stages() {
+    return (SWAP ? SMEM_BUDGET_SWAP : SMEM_BUDGET_BIG) / stage_bytes<BN>();
 }
-template <int BN> constexpr int smem_bytes() { return num_stages<BN>() * stage_bytes<BN>() + 1024 + 256; }
+template <int BN, bool SWAP> constexpr int smem_bytes() { return num_stages<BN, SWAP>() * stage_bytes<BN>() + 1024 + 256; }
 
 __device__ __forceinline__ void store_out(const Epilogue& ep, int m, int n, float v) {
     if (ep.bias) v += load_as_f32(ep.bias, ep.bias_dtype, n);
@@ -52,10 +55,11 @@ __device__ __forceinline__ void store_out(const Epilogue& ep, int m, int n, floa
 }
 
 template <int BN, bool SWAP>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
-               const Epilogue ep, const int K, int32_t* __restrict__ status) {
-    constexpr int STAGES = num_stages<BN>();
+               const Epilogue ep, const int K, float* __restrict__ ws, int32_t* __restrict__ counters,
+               int32_t* __restrict__ status) {
+    constexpr int STAGES = num_stages<BN, SWAP>();
     constexpr int STAGE = stage_bytes<BN>();
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
     constexpr int CH = BN < 32 ? 16 : 32;             // accumulator columns read per tcgen05.ld
@@ -67,11 +71,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     uint64_t* acc_ready = empty + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
     volatile uint32_t* aborted = tmem_slot + 1;
+    volatile uint32_t* last_flag = tmem_slot + 2;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p0 = blockIdx.x * BM;                   // first row of the M-side operand
     const int q0 = blockIdx.y * BN;                   // first row of the N-side operand
-    const int num_kb = (K + BK - 1) / BK;
+    // split-K: CTA z of gridDim.z accumulates k-blocks [kb_begin, kb_end)
+    const int total_kb = (K + BK - 1) / BK;
+    const int splits = gridDim.z;
+    const int kb_begin = (int)((long long)blockIdx.z * total_kb / splits);
+    const int num_kb = (int)((long long)(blockIdx.z + 1) * total_kb / splits) - kb_begin;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -95,8 +104,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 101); *aborted = 1; break; }
                 uint8_t* tile = smem + s * STAGE;
                 mbar_expect_tx(&full[s], STAGE);
-                tma_load_2d(tile, &map_p, &full[s], kb * BK, p0);
-                tma_load_2d(tile + BM * BK * 2, &map_q, &full[s], kb * BK, q0);
+                tma_load_2d(tile, &map_p, &full[s], (kb_begin + kb) * BK, p0);
+                tma_load_2d(tile + BM * BK * 2, &map_q, &full[s], (kb_begin + kb) * BK, q0);
             }
         }
     } else if (warp == 1) {
@@ -126,30 +135,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         if (!ok) atomicExch(status, 103);
         ok = ok && *aborted == 0;
         tc_fence_after_sync();
-        const int p = p0 + quad * 32 + lane;          // this thread's row of the M-side operand
-        if (ok) {
+        const int r = quad * 32 + lane;               // this thread's TMEM lane
+        const int p = p0 + r;                         // its row of the M-side operand
+        auto emit = [&](int c, const float (&v)[CH]) {
+            if constexpr (!SWAP) {
+                if (p < ep.M) {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        const int n = q0 + c * CH + j;
+                        if (n < ep.N) store_out(ep, p, n, v[j]);
+                    }
+                }
+            } else {
+                if (p < ep.N) {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        const int m = q0 + c * CH + j;
+                        if (m < ep.M) store_out(ep, m, p, v[j]);
+                    }
+                }
+            }
+        };
+        if (splits == 1) {
+            if (ok) {
+#pragma unroll 1
+                for (int c = 0; c < BN / CH; ++c) {
+                    uint32_t raw[CH];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * CH);
+                    if constexpr (CH == 32) tmem_load_32x32(taddr, raw); else tmem_load_32x16(taddr, raw);
+                    tmem_load_wait();
+                    float v[CH];
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(raw[j]);
+                    emit(c, v);
+                }
+            }
+        } else {
+            // Split-K: every slice leaves its 32-bit partial tile in the workspace; the CTA that arrives
+            // last adds the slices in slice order (its own included, read back like the others), so the
+            // sum does not depend on which CTA finished when.
+            const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+            float* mine = ws + ((tile * splits + blockIdx.z) * BN) * BM;
 #pragma unroll 1
             for (int c = 0; c < BN / CH; ++c) {
-                uint32_t r[CH];
+                uint32_t raw[CH];
                 const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * CH);
-                if constexpr (CH == 32) tmem_load_32x32(taddr, r); else tmem_load_32x16(taddr, r);
+                if constexpr (CH == 32) tmem_load_32x32(taddr, raw); else tmem_load_32x16(taddr, raw);
                 tmem_load_wait();
-                if constexpr (!SWAP) {
-                    if (p < ep.M) {
 #pragma unroll
-                        for (int j = 0; j < CH; ++j) {
-                            const int n = q0 + c * CH + j;
-                            if (n < ep.N) store_out(ep, p, n, __uint_as_float(r[j]));
-                        }
-                    }
-                } else {
-                    if (p < ep.N) {
+                for (int j = 0; j < CH; ++j) mine[(size_t)(c * CH + j) * BM + r] = ok ? __uint_as_float(raw[j]) : 0.f;
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps
+            if (threadIdx.x == 64) {
+                const int prev = atomicAdd(&counters[tile], 1);
+                *last_flag = (prev == splits - 1) ? 1u : 0u;
+                if (prev == splits - 1) counters[tile] = 0;           // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (*last_flag) {
+                __threadfence();
+#pragma unroll 1
+                for (int c = 0; c < BN / CH; ++c) {
+                    float v[CH];
 #pragma unroll
-                        for (int j = 0; j < CH; ++j) {
-                            const int m = q0 + c * CH + j;
-                            if (m < ep.M) store_out(ep, m, p, __uint_as_float(r[j]));
-                        }
+                    for (int j = 0; j < CH; ++j) v[j] = 0.f;
+                    for (int z = 0; z < splits; ++z) {
+                        const float* part = ws + ((tile * splits + z) * BN) * BM;
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) v[j] += __ldcg(&part[(size_t)(c * CH + j) * BM + r]);
                     }
+                    emit(c, v);
                 }
             }
         }
@@ -220,19 +276,29 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
     return QS_OK;
 }
 
+// How many split-K slices the weight-streaming arrangement uses: a function of N and K only, never of
+// the number of tokens, so that a token's result does not depend on its batch.
+int choose_splits(int N, int K) {
+    const int tiles = (N + BM - 1) / BM;
+    const int total_kb = (K + BK - 1) / BK;
+    int splits = (TARGET_CTAS + tiles / 2) / tiles;
+    if (splits > total_kb / MIN_KB_PER_SPLIT) splits = total_kb / MIN_KB_PER_SPLIT;
+    return splits < 1 ? 1 : splits;
+}
+
 template <int BN, bool SWAP>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Epilogue& ep, int p_rows, int q_rows, int K,
-           int32_t* status, cudaStream_t stream) {
+           int splits, float* ws, int32_t* counters, int32_t* status, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             smem_bytes<BN>());
+                                             smem_bytes<BN, SWAP>());
         if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc: shared memory of %d bytes refused: %s",
-                                             smem_bytes<BN>(), cudaGetErrorString(e));
+                                             smem_bytes<BN, SWAP>(), cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((p_rows + BM - 1) / BM, (q_rows + BN - 1) / BN);
-    gemm_tc_kernel<BN, SWAP><<<grid, THREADS, smem_bytes<BN>(), stream>>>(mp, mq, ep, K, status);
+    dim3 grid((p_rows + BM - 1) / BM, (q_rows + BN - 1) / BN, splits);
+    gemm_tc_kernel<BN, SWAP><<<grid, THREADS, smem_bytes<BN, SWAP>(), stream>>>(mp, mq, ep, K, ws, counters, status);
     return qs_check_launch("gemm_tc");
 }
 
@@ -241,9 +307,13 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Epilogue& ep, int
 // A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16 contiguous; C: [M, N] bfloat16 or float32.
 // res1/res2: bfloat16 [M, N] with row stride ldr, or null.  status: device int32 that receives a
 // non-zero code if a bounded wait inside the kernel ran out.
+// ws / counters: scratch for split-K in the weight-streaming arrangement (M <= 64): `ws_floats` floats
+// and `n_counters` int32 that are ZERO before the first call (the kernel leaves them zero).  Without
+// them (null) the product runs unsplit.  Calls that share the scratch must not overlap on the GPU.
 QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const void* bias, int bias_dtype, int act,
                       const void* res1, const void* res2, int M, int N, int K, long long lda, long long ldc,
-                      long long ldr, int32_t* status, cudaStream_t stream) {
+                      long long ldr, float* ws, long long ws_floats, int32_t* counters, int n_counters,
+                      int32_t* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return QS_OK;
     QS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     QS_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc: K=%d and the row stride %lld must be multiples of 8", K, lda);
@@ -256,12 +326,15 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
         QS_REQUIRE((M + BM - 1) / BM <= 65535 * 1 && (N + 127) / 128 <= 65535, "gemm_tc: sizes exceed the grid");
         if ((rc = tensor_map(&ma, A, M, K, lda, BM)) != QS_OK) return rc;
         if ((rc = tensor_map(&mw, W, N, K, K, 128)) != QS_OK) return rc;
-        return launch<128, false>(ma, mw, ep, M, N, K, status, stream);
+        return launch<128, false>(ma, mw, ep, M, N, K, 1, nullptr, nullptr, status, stream);
     }
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    int splits = choose_splits(N, K);
+    const long long tiles = (N + BM - 1) / BM;
+    if (!ws || !counters || tiles > n_counters || tiles * splits * 64 * BM > ws_floats) splits = 1;
     if ((rc = tensor_map(&mw, W, N, K, K, BM)) != QS_OK) return rc;
     if ((rc = tensor_map(&ma, A, M, K, lda, bn)) != QS_OK) return rc;
-    if (bn == 16) return launch<16, true>(mw, ma, ep, N, M, K, status, stream);
-    if (bn == 32) return launch<32, true>(mw, ma, ep, N, M, K, status, stream);
-    return launch<64, true>(mw, ma, ep, N, M, K, status, stream);
+    if (bn == 16) return launch<16, true>(mw, ma, ep, N, M, K, splits, ws, counters, status, stream);
+    if (bn == 32) return launch<32, true>(mw, ma, ep, N, M, K, splits, ws, counters, status, stream);
+    return launch<64, true>(mw, ma, ep, N, M, K, splits, ws, counters, status, stream);
 }

@@ -17,7 +17,7 @@ def _entry():
     if _fn is None:
         _fn = ops.bind("qs_gemm_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                                      c_void_p, c_void_p])
+                                      c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
     return _fn
 
 
@@ -27,6 +27,21 @@ def status_word(device) -> torch.Tensor:
     if key not in _status:
         _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[key]
+
+
+WS_FLOATS = 16 << 20            # split-K partial tiles: 64 MiB of float32
+N_COUNTERS = 1 << 16
+_scratch = {}
+
+
+def scratch(device):
+    """Per-device scratch of the split-K reduction: partial tiles and zeroed arrival counters.
+    Shared by all calls on the device, which run on one stream."""
+    key = (device.type, device.index)
+    if key not in _scratch:
+        _scratch[key] = (torch.empty(WS_FLOATS, dtype=torch.float32, device=device),
+                         torch.zeros(N_COUNTERS, dtype=torch.int32, device=device))
+    return _scratch[key]
 
 
 def check_status(device) -> None:
@@ -60,8 +75,10 @@ def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None) 
     if len(res) == 2 and res[0].stride(0) != res[1].stride(0):
         raise QStreamError(QsError.INVALID_INPUT, "linear: residuals of two layouts")
     res += [None, None]
+    ws, counters = scratch(x.device)
     ops.check(_entry()(ops.ptr(out), ops.dtype_code(out), ops.ptr(x), ops.ptr(weight), ops.ptr(bias),
                        ops.dtype_code(bias) if bias is not None else 0, ops.ACTIVATIONS[activation],
                        ops.ptr(res[0]), ops.ptr(res[1]), M, N, K, x.stride(0), N, ldr,
+                       ops.ptr(ws), ws.numel(), ops.ptr(counters), counters.numel(),
                        ops.ptr(status_word(x.device)), ops.stream()))
     return out

@@ -64,8 +64,30 @@ def test_strided_input_and_row_independence():
     whole = gemm_tc.linear(x, w, out_dtype=torch.float32)
     np.testing.assert_allclose(f64(whole), f64(x) @ f64(w).T, atol=2e-3, rtol=2e-3)
     # one row's result is the same bits in a batch of 90 (tokens on the M side) and of 2, 20, 50
-    # (tokens on the N side): one TMEM cell per element, products summed in ascending k
+    # (tokens on the N side): one TMEM cell per element, products summed in ascending k (K is too
+    # short here for split-K)
     for rows in (slice(7, 9), slice(10, 30), slice(40, 90)):
         part = gemm_tc.linear(x[rows], w, out_dtype=torch.float32)
         assert torch.equal(part, whole[rows])
+    gemm_tc.check_status(x.device)
+
+
+@pytest.mark.parametrize("N,K", [(256, 4096), (4096, 4096), (520, 16384), (12288, 1024)])
+def test_split_k_is_exact_and_does_not_depend_on_the_batch(N, K):
+    """Few tokens and a long K: the product is cut along K over several CTAs whose partial tiles are
+    added in slice order.  The result must match float64, be the same bits on every call, and a
+    token's row must not depend on how many other tokens came with it."""
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn(64, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
+    bias = torch.randn(N, generator=g).bfloat16().cuda()
+    res = torch.randn(64, N, generator=g).bfloat16().cuda()
+    whole = gemm_tc.linear(x, w, bias, "gelu_new", (res,), torch.float32)
+    ref = P.gelu_new(f64(x) @ f64(w).T + f64(bias)) + f64(res)
+    np.testing.assert_allclose(f64(whole), ref, atol=3e-3, rtol=3e-3)
+    for _ in range(3):
+        assert torch.equal(gemm_tc.linear(x, w, bias, "gelu_new", (res,), torch.float32), whole)
+    for rows in (slice(0, 1), slice(5, 13), slice(30, 62), slice(3, 40)):
+        part = gemm_tc.linear(x[rows], w, bias, "gelu_new", (res[rows],), torch.float32)
+        assert torch.equal(part, whole[rows]), rows
     gemm_tc.check_status(x.device)
