@@ -61,8 +61,11 @@ class KvGroup:
         self.pool = PagePool(n_pages)
         self.max_pages = max_pages
         shape = (len(self.entries), n_pages, need.n_kv_heads, page_tokens, need.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        # Zeroed once: the tensor-core prefill kernel multiplies a page's rows beyond the sequence's end by
+        # weights of exactly 0, which must not meet non-finite leftovers.  Pages are not cleared again
+        # when they change hands: what the kernels wrote there is finite.
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
         self.table_host = np.full((n_slots, max_pages), -1, dtype=np.int32)
         self.table_dev = torch.full((n_slots, max_pages), -1, dtype=torch.int32, device=device)
         self._dirty: set[int] = set()

@@ -141,6 +141,28 @@ __device__ __forceinline__ void tmem_load_32x16(uint32_t taddr, uint32_t (&r)[16
         : "memory");
 }
 
+// Store 32 lanes x 32 columns of 32-bit (the mirror of tmem_load_32x32).
+__device__ __forceinline__ void tmem_store_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_store_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Make shared-memory writes of this thread visible to the async proxy (TMA, tcgen05.mma operands).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void tmem_load_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -163,11 +185,30 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
     return d;
 }
 
+// The same for an MN-major operand (rows of the K dimension in memory, the M or N dimension contiguous)
+// as TMA's 128-byte swizzle writes a [k rows][64 elements] box: 64 contiguous elements of M/N per
+// 128-byte row, eight k-rows per 1024-byte group.  Leading byte offset = distance between successive
+// 64-element blocks along M/N; stride byte offset = distance between successive 8-row groups along K.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((leading_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((stride_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
 // Instruction descriptor of kind::f16 with bfloat16 A and B (both K-major), float32 D:
 // [4,6) D format 1 = F32, [7,10) A format 1 = BF16, [10,13) B format 1 = BF16, bit 15/16 A/B
 // major 0 = K, [17,23) N >> 3, [24,29) M >> 4.
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(int M, int N) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// The same with B stored MN-major (bit 16).
+__host__ __device__ constexpr uint32_t idesc_bf16_f32_b_mn(int M, int N) {
+    return idesc_bf16_f32(M, N) | (1u << 16);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread.

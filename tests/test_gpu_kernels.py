@@ -84,7 +84,7 @@ def test_linear_simt_row_does_not_depend_on_batch():
 class PagedCase:
     """Sequences laid into a paged cache through shuffled pages."""
 
-    def __init__(self, dtype, lens, H, Hkv, dh, page_tokens=64, seed=0, n_slots=6):
+    def __init__(self, dtype, lens, H, Hkv, dh, page_tokens=64, seed=0, n_slots=6, fill=float("nan")):
         g = torch.Generator().manual_seed(seed)
         self.dtype, self.lens, self.H, self.Hkv, self.dh, self.pt = dtype, lens, H, Hkv, dh, page_tokens
         max_pages = max(-(-n // page_tokens) for n in lens) + 1
@@ -95,8 +95,8 @@ class PagedCase:
         for s, n in zip(self.slots, lens):
             for i in range(-(-n // page_tokens)):
                 self.table[s, i] = perm.pop()
-        self.k_cache = torch.full((n_pages, Hkv, page_tokens, dh), float("nan"), dtype=DT[dtype]).cuda()
-        self.v_cache = torch.full((n_pages, Hkv, page_tokens, dh), float("nan"), dtype=DT[dtype]).cuda()
+        self.k_cache = torch.full((n_pages, Hkv, page_tokens, dh), fill, dtype=DT[dtype]).cuda()
+        self.v_cache = torch.full((n_pages, Hkv, page_tokens, dh), fill, dtype=DT[dtype]).cuda()
         self.q = [torch.randn(n, H, dh, generator=g).to(DT[dtype]) for n in lens]
         self.k = [torch.randn(n, Hkv, dh, generator=g).to(DT[dtype]) for n in lens]
         self.v = [torch.randn(n, Hkv, dh, generator=g).to(DT[dtype]) for n in lens]
@@ -306,3 +306,72 @@ def test_decode_attention_does_not_depend_on_the_batch():
         alone = attention_bf16.decode(ql[i:i + 1], *args, slot_l[i:i + 1], pos_l[i:i + 1], tdev, case.pt,
                                       case.k_cache, case.v_cache, 2048, case.status)
         assert torch.equal(alone[0], both[i])
+
+
+def _tiles(ranges, slots):
+    tiles, row = [], 0
+    for i, a, b in ranges:
+        for t in range(a, b, 128):
+            tiles.append((row + t - a, min(128, b - t), t, slots[i]))
+        row += b - a
+    tiles.sort(key=lambda t: -(t[2] + t[1]))
+    return torch.tensor(tiles, dtype=torch.int32).cuda()
+
+
+@pytest.mark.parametrize("H,Hkv,dh,window", [(2, 2, 64, 0), (16, 16, 256, 0), (4, 4, 16, 0), (6, 2, 48, 0), (2, 1, 80, 0),
+                                             (3, 3, 128, 0), (2, 2, 192, 0), (4, 4, 64, 100), (2, 2, 32, 1),
+                                             (2, 2, 256, 200)])
+def test_prefill_attention_kernel(H, Hkv, dh, window):
+    """The tensor-core prefill kernel (bfloat16) against the plain attention: whole prompts of unequal
+    lengths in one packed step (page and tile edges, a single token), then a second chunk of each
+    sequence on top of the cached first one, with grouped heads, padded head sizes and windows."""
+    from qstream_b200.csrc import attention_bf16
+    lens = [1, 64, 129, 300, 700]
+    case = PagedCase("bfloat16", lens, H, Hkv, dh, seed=dh + window, n_slots=7, fill=0.0)
+    case.v_cache.fill_(1e30)                    # rows beyond a sequence's end: finite leftovers must not matter
+    tdev = case.table.cuda()
+    outs = [[] for _ in lens]
+    cuts = [(0, max(1, n * 2 // 3)) for n in lens]
+    for phase in range(2):
+        ranges = [(i, a, b) for i, (a, b) in enumerate(cuts) if b > a]
+        q, k, v, slot, pos = case.packed(ranges)
+        ops.rope_store(None, k, v, 0, Hkv, dh, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+        o = attention_bf16.prefill(q, H, Hkv, dh, dh ** -0.5, window, _tiles(ranges, case.slots), tdev, case.pt,
+                                   case.k_cache, case.v_cache, case.status)
+        gen = ops.attention(q, H, Hkv, dh, dh ** -0.5, window, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+        np.testing.assert_allclose(f64(o), f64(gen), atol=3e-2, rtol=3e-2)
+        row = 0
+        for i, a, b in ranges:
+            outs[i].append(o[row:row + b - a].cpu())
+            row += b - a
+        cuts = [(b, n) for (a, b), n in zip(cuts, lens)]
+    torch.cuda.synchronize()
+    assert int(case.status.item()) == 0
+    for i, n in enumerate(lens):
+        ref = P.causal_attention(f64(case.q[i]), f64(case.k[i]), f64(case.v[i]), window)
+        np.testing.assert_allclose(f64(torch.cat(outs[i])), ref, atol=3e-2, rtol=3e-2, err_msg=f"sequence {i} of {n}")
+
+
+def test_prefill_attention_finds_one_far_key_and_keeps_rows_apart():
+    from qstream_b200.csrc import attention_bf16
+    H, dh, n = 2, 64, 600
+    for far, window in ((0, 0), (63, 0), (64, 0), (599, 0), (500, 100), (501, 100)):
+        case = PagedCase("bfloat16", [n], H, H, dh, seed=far, fill=0.0)
+        case.q[0][:] = 0
+        case.k[0][:] = 0
+        case.q[0][n - 1, :, 0] = 12.0
+        case.k[0][far, :, 0] = 12.0
+        q, k, v, slot, pos = case.packed([(0, 0, n)])
+        tdev = case.table.cuda()
+        ops.rope_store(None, k, v, 0, H, dh, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+        o = attention_bf16.prefill(q, H, H, dh, dh ** -0.5, window, _tiles([(0, 0, n)], case.slots), tdev, case.pt,
+                                   case.k_cache, case.v_cache, case.status)
+        got = f64(o[n - 1]).reshape(H, dh)
+        if window == 0 or far > n - 1 - window:
+            np.testing.assert_allclose(got, f64(case.v[0][far]), atol=5e-2)
+        else:
+            np.testing.assert_allclose(got, f64(case.v[0][n - window:n]).mean(0), atol=5e-2)
+        # every other row has all-zero scores: the mean of its visible values
+        t = 300
+        lo = 0 if window == 0 else t - window + 1
+        np.testing.assert_allclose(f64(o[t]).reshape(H, dh), f64(case.v[0][lo:t + 1]).mean(0), atol=5e-2)
