@@ -25,51 +25,50 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
                                   const int32_t* __restrict__ page_table, int max_pages, int page_shift,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   int32_t* __restrict__ status) {
+    // one block per token; its threads walk over all (head, pair of dims) of q, then k, then v
     const int t = blockIdx.x;
     const int slot = tok_slot[t];
     if (slot < 0) return;
     const int pos = tok_pos[t];
-    const int head = blockIdx.y;            // [0, n_heads): q; then k heads; then v heads
     const int page_tokens = 1 << page_shift;
     const bool rotate = cos_sin != nullptr && R > 0;
     if (rotate && (pos < 0 || pos >= max_pos)) { if (threadIdx.x == 0) atomicExch(status, 1); return; }
     const float* cs = rotate ? cos_sin + (size_t)pos * R : nullptr;      // R/2 pairs of (cos, sin)
+    const int half = dh >> 1;
 
-    size_t cache_row = 0;
-    if (head >= n_heads) {
-        const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
-        if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
-        const int kvh = (head - n_heads) % n_kv_heads;
-        cache_row = (((size_t)page * n_kv_heads + kvh) * page_tokens + (pos & (page_tokens - 1))) * dh;
+    if (q && rotate) {
+        const int rp = R >> 1;                                           // rotated pairs per head
+        for (int e = threadIdx.x; e < n_heads * rp; e += blockDim.x) {
+            const int head = e / rp, j = e - head * rp;
+            T* row = q + (size_t)t * ldq + (size_t)head * dh;
+            const float c = cs[2 * j], sn = cs[2 * j + 1];
+            const float a = to_f32(row[2 * j]), b = to_f32(row[2 * j + 1]);
+            row[2 * j] = from_f32<T>(a * c - b * sn);
+            row[2 * j + 1] = from_f32<T>(a * sn + b * c);
+        }
     }
-
-    if (head < n_heads) {
-        if (!q || !rotate) return;
-        T* row = q + (size_t)t * ldq + (size_t)head * dh;
-        for (int j = threadIdx.x; 2 * j < R; j += blockDim.x) {
-            const float c = cs[2 * j], s = cs[2 * j + 1];
-            const float a = to_f32(row[2 * j]), b = to_f32(row[2 * j + 1]);
-            row[2 * j] = from_f32<T>(a * c - b * s);
-            row[2 * j + 1] = from_f32<T>(a * s + b * c);
+    if (n_kv_heads == 0) return;
+    const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
+    if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
+    const size_t in_page = (size_t)(pos & (page_tokens - 1)) * dh;
+    for (int e = threadIdx.x; e < n_kv_heads * half; e += blockDim.x) {
+        const int kvh = e / half, j = e - kvh * half;
+        const size_t dst_off = ((size_t)page * n_kv_heads + kvh) * page_tokens * dh + in_page;
+        const T* krow = k + (size_t)t * ldk + (size_t)kvh * dh;
+        T* kdst = k_cache + dst_off;
+        if (rotate && 2 * j < R) {
+            const float c = cs[2 * j], sn = cs[2 * j + 1];
+            const float a = to_f32(krow[2 * j]), b = to_f32(krow[2 * j + 1]);
+            kdst[2 * j] = from_f32<T>(a * c - b * sn);
+            kdst[2 * j + 1] = from_f32<T>(a * sn + b * c);
+        } else {
+            kdst[2 * j] = krow[2 * j];
+            kdst[2 * j + 1] = krow[2 * j + 1];
         }
-    } else if (head < n_heads + n_kv_heads) {
-        const T* row = k + (size_t)t * ldk + (size_t)(head - n_heads) * dh;
-        T* dst = k_cache + cache_row;
-        for (int j = threadIdx.x; 2 * j < dh; j += blockDim.x) {
-            const float a = to_f32(row[2 * j]), b = to_f32(row[2 * j + 1]);
-            if (rotate && 2 * j < R) {
-                const float c = cs[2 * j], s = cs[2 * j + 1];
-                dst[2 * j] = from_f32<T>(a * c - b * s);
-                dst[2 * j + 1] = from_f32<T>(a * s + b * c);
-            } else {
-                dst[2 * j] = row[2 * j];
-                dst[2 * j + 1] = row[2 * j + 1];
-            }
-        }
-    } else {
-        const T* row = v + (size_t)t * ldv + (size_t)(head - n_heads - n_kv_heads) * dh;
-        T* dst = v_cache + cache_row;
-        for (int j = threadIdx.x; j < dh; j += blockDim.x) dst[j] = row[j];
+        const T* vrow = v + (size_t)t * ldv + (size_t)kvh * dh;
+        T* vdst = v_cache + dst_off;
+        vdst[2 * j] = vrow[2 * j];
+        vdst[2 * j + 1] = vrow[2 * j + 1];
     }
 }
 
@@ -203,11 +202,11 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
     QS_REQUIRE(dh % 2 == 0, "rope_store: head size %d must be even", dh);
     QS_REQUIRE(R >= 0 && R % 2 == 0 && R <= dh, "rope_store: rotary width %d must be even and within the head size %d", R, dh);
     QS_REQUIRE(page_tokens > 0 && (page_tokens & (page_tokens - 1)) == 0, "rope_store: page size %d is no power of two", page_tokens);
-    QS_REQUIRE(n_heads + 2 * n_kv_heads <= 65535, "rope_store: too many heads");
     int shift = 0;
     while ((1 << shift) < page_tokens) ++shift;
-    dim3 grid(T_tokens, n_heads + 2 * n_kv_heads);
-    const int threads = dh >= 256 ? 128 : (dh >= 128 ? 64 : 32);
+    dim3 grid(T_tokens);
+    const int work = (n_heads + 2 * n_kv_heads) * dh / 2;
+    const int threads = work >= 2048 ? 256 : (work >= 512 ? 128 : 64);
     if (dtype == QS_F32)
         rope_store_kernel<float><<<grid, threads, 0, stream>>>((float*)q, (const float*)k, (const float*)v,
             (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos,

@@ -103,7 +103,8 @@ QS_API int qs_layernorm(void* out, const void* x, int dtype, const void* w, int 
     const size_t smem = (size_t)D * sizeof(float);
     QS_REQUIRE(smem <= 200 * 1024, "layernorm: width %d does not fit one block's shared memory (max %d)",
                D, 200 * 1024 / 4);
-    const int threads = D >= 4096 ? 1024 : (D >= 2048 ? 512 : (D >= 512 ? 256 : 128));
+    // few rows: many threads per row for latency; many rows: smaller blocks, more rows per SM
+    const int threads = rows >= 512 ? (D >= 1024 ? 256 : 128) : (D >= 4096 ? 1024 : (D >= 2048 ? 512 : (D >= 512 ? 256 : 128)));
     cudaError_t e = cudaSuccess;
     if (dtype == QS_F32) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

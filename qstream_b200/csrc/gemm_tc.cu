@@ -215,6 +215,166 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ----------------------------------------------------------------------------- persistent kernel (many tokens)
+
+// Wait that also gives up when another role of the CTA has recorded a failure.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* aborted) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *aborted) return false;
+    }
+    return false;
+}
+
+template <int BN> constexpr int p_stages() { return SMEM_BUDGET_BIG / stage_bytes<BN>(); }
+template <int BN> constexpr int p_smem_bytes() { return p_stages<BN>() * stage_bytes<BN>() + 1024 + 512; }
+
+// One CTA per SM walks over output tiles of 128 x BN (tile t = n_tile * m_tiles + m_tile, so CTAs that
+// run together share rows of W and all of A stays in L2).  Two accumulators in TMEM: while the four
+// epilogue warps drain tile i, the MMA warp already accumulates tile i + 1 into the other one, and the
+// TMA producer runs ahead across tile borders through the same ring of stages.
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                          const Epilogue ep, const int K, const int m_tiles, const int n_tiles,
+                          int32_t* __restrict__ status) {
+    constexpr int STAGES = p_stages<BN>();
+    constexpr int STAGE = stage_bytes<BN>();
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;              // [2]
+    uint64_t* acc_empty = acc_full + 2;               // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* aborted = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (K + BK - 1) / BK;
+    const int total_tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+        *aborted = 0;
+        mbar_fence_init();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_w);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t it = 0;
+            for (int t = blockIdx.x; t < total_tiles && !*aborted; t += gridDim.x) {
+                const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!wait_or_abort(&empty[s], ((it / STAGES) & 1) ^ 1, aborted)) { atomicExch(status, 121); *aborted = 1; break; }
+                    uint8_t* tile = smem + s * STAGE;
+                    mbar_expect_tx(&full[s], STAGE);
+                    tma_load_2d(tile, &map_a, &full[s], kb * BK, m0);
+                    tma_load_2d(tile + BM * BK * 2, &map_w, &full[s], kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+            uint32_t it = 0;
+            int i = 0;
+            for (int t = blockIdx.x; t < total_tiles && !*aborted; t += gridDim.x, ++i) {
+                const int buf = i & 1;
+                if (!wait_or_abort(&acc_empty[buf], ((i >> 1) & 1) ^ 1, aborted)) { atomicExch(status, 122); *aborted = 1; break; }
+                tc_fence_after_sync();
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!wait_or_abort(&full[s], (it / STAGES) & 1, aborted)) { atomicExch(status, 123); *aborted = 1; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE);
+                    const uint64_t da = smem_desc_sw128(a_addr);
+                    const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        mma_bf16(tmem_base + (uint32_t)(buf * BN), da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    mma_commit(&empty[s]);
+                }
+                mma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const bool vec_ok = ep.c_dtype == QS_BF16 && (ep.ldc % 8) == 0 && ((uintptr_t)ep.C % 16) == 0 &&
+                            (!ep.res1 || ((ep.ldr % 8) == 0 && ((uintptr_t)ep.res1 % 16) == 0)) &&
+                            (!ep.res2 || ((uintptr_t)ep.res2 % 16) == 0);
+        int i = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            const int m = (t % m_tiles) * BM + r, n0 = (t / m_tiles) * BN;
+            if (!wait_or_abort(&acc_full[buf], (i >> 1) & 1, aborted)) { atomicExch(status, 124); *aborted = 1; break; }
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t raw[32];
+                tmem_load_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c * 32), raw);
+                tmem_load_wait();
+                const int nc = n0 + c * 32;
+                if (m >= ep.M || nc >= ep.N) continue;
+                if (vec_ok && nc + 32 <= ep.N) {
+                    // 32 consecutive outputs of one row: bias and activation on the accumulator, residuals
+                    // added in 32-bit, one rounding, four 16-byte stores
+                    __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(ep.C) + (size_t)m * ep.ldc + nc;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float x = __uint_as_float(raw[g * 8 + j]);
+                            if (ep.bias) x += load_as_f32(ep.bias, ep.bias_dtype, nc + g * 8 + j);
+                            v[j] = apply_activation(x, ep.act);
+                        }
+                        if (ep.res1) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + nc + g * 8);
+                            const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u); }
+                        }
+                        if (ep.res2) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res2 + (size_t)m * ep.ldr + nc + g * 8);
+                            const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u); }
+                        }
+                        uint32_t o[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const __nv_bfloat162 pb = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            o[j] = *reinterpret_cast<const uint32_t*>(&pb);
+                        }
+                        *reinterpret_cast<uint4*>(crow + g * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (nc + j < ep.N) store_out(ep, m, nc + j, __uint_as_float(raw[j]));
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 // ----------------------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -302,6 +462,28 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Epilogue& ep, int
     return qs_check_launch("gemm_tc");
 }
 
+template <int BN>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const Epilogue& ep, int M, int N, int K,
+                      int32_t* status, cudaStream_t stream) {
+    static bool configured = false;
+    static int sm_count = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             p_smem_bytes<BN>());
+        int dev = 0;
+        if (e == cudaSuccess) e = cudaGetDevice(&dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc: set-up of the persistent kernel failed: %s",
+                                             cudaGetErrorString(e));
+        configured = true;
+    }
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    const long long total = (long long)m_tiles * n_tiles;
+    const int grid = (int)(total < sm_count ? total : sm_count);
+    gemm_tc_persistent_kernel<BN><<<grid, THREADS, p_smem_bytes<BN>(), stream>>>(ma, mw, ep, K, m_tiles, n_tiles, status);
+    return qs_check_launch("gemm_tc persistent");
+}
+
 }  // namespace
 
 // A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16 contiguous; C: [M, N] bfloat16 or float32.
@@ -325,8 +507,10 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
     if (M > 64) {
         QS_REQUIRE((M + BM - 1) / BM <= 65535 * 1 && (N + 127) / 128 <= 65535, "gemm_tc: sizes exceed the grid");
         if ((rc = tensor_map(&ma, A, M, K, lda, BM)) != QS_OK) return rc;
-        if ((rc = tensor_map(&mw, W, N, K, K, 128)) != QS_OK) return rc;
-        return launch<128, false>(ma, mw, ep, M, N, K, 1, nullptr, nullptr, status, stream);
+        const int bn = N > 128 ? 256 : 128;
+        if ((rc = tensor_map(&mw, W, N, K, K, bn)) != QS_OK) return rc;
+        if (bn == 256) return launch_persistent<256>(ma, mw, ep, M, N, K, status, stream);
+        return launch_persistent<128>(ma, mw, ep, M, N, K, status, stream);
     }
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     int splits = choose_splits(N, K);
