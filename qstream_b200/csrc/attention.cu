@@ -25,8 +25,9 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
                                   const int32_t* __restrict__ page_table, int max_pages, int page_shift,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   int32_t* __restrict__ status) {
-    // one block per token; its threads walk over all (head, pair of dims) of q, then k, then v
+    // blockIdx.x = token; the gridDim.y blocks of a token share its (head, pair of dims) items of q, then k and v
     const int t = blockIdx.x;
+    const int tid = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
     const int slot = tok_slot[t];
     if (slot < 0) return;
     const int pos = tok_pos[t];
@@ -38,7 +39,7 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
 
     if (q && rotate) {
         const int rp = R >> 1;                                           // rotated pairs per head
-        for (int e = threadIdx.x; e < n_heads * rp; e += blockDim.x) {
+        for (int e = tid; e < n_heads * rp; e += stride) {
             const int head = e / rp, j = e - head * rp;
             T* row = q + (size_t)t * ldq + (size_t)head * dh;
             const float c = cs[2 * j], sn = cs[2 * j + 1];
@@ -51,7 +52,7 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
     const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
     if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
     const size_t in_page = (size_t)(pos & (page_tokens - 1)) * dh;
-    for (int e = threadIdx.x; e < n_kv_heads * half; e += blockDim.x) {
+    for (int e = tid; e < n_kv_heads * half; e += stride) {
         const int kvh = e / half, j = e - kvh * half;
         const size_t dst_off = ((size_t)page * n_kv_heads + kvh) * page_tokens * dh + in_page;
         const T* krow = k + (size_t)t * ldk + (size_t)kvh * dh;
@@ -204,9 +205,11 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
     QS_REQUIRE(page_tokens > 0 && (page_tokens & (page_tokens - 1)) == 0, "rope_store: page size %d is no power of two", page_tokens);
     int shift = 0;
     while ((1 << shift) < page_tokens) ++shift;
-    dim3 grid(T_tokens);
     const int work = (n_heads + 2 * n_kv_heads) * dh / 2;
     const int threads = work >= 2048 ? 256 : (work >= 512 ? 128 : 64);
+    int per_token = 1;                       // few tokens (decode): several blocks per token
+    if (T_tokens < 256) { per_token = (n_kv_heads * dh / 2 + threads - 1) / threads; if (per_token > 16) per_token = 16; if (per_token < 1) per_token = 1; }
+    dim3 grid(T_tokens, per_token);
     if (dtype == QS_F32)
         rope_store_kernel<float><<<grid, threads, 0, stream>>>((float*)q, (const float*)k, (const float*)v,
             (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos,

@@ -200,6 +200,7 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
 __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo, const float* __restrict__ partial,
                                     const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                                     int n_heads, int dh, int window, int max_splits) {
+    grid_dep_launch();
     const int head = blockIdx.x, t = blockIdx.y;
     __nv_bfloat16* o = out + (size_t)t * ldo + (size_t)head * dh;
     if (tok_slot[t] < 0) {

@@ -25,6 +25,33 @@ int qs_check_launch(const char* what);
 
 #define QS_REQUIRE(cond, ...) do { if (!(cond)) return qs_fail(QS_ERR_INVALID_INPUT, __VA_ARGS__); } while (0)
 
+// Programmatic dependent launch.  A kernel calls `grid_dep_launch()` once it no longer minds the next
+// kernel of the stream being scheduled beside it, and a kernel launched with `qs_launch_dependent`
+// calls `grid_dep_wait()` before it first touches memory the previous kernel wrote (or writes memory
+// the previous kernel read): what precedes the wait - barrier set-up, TMEM allocation, loads of
+// weights that no kernel writes - overlaps the previous kernel's tail.  Every such kernel executes the
+// wait before it ends, so completion of a kernel implies completion of all kernels before it.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+cudaError_t qs_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -72,6 +72,7 @@ __global__ void layernorm_kernel(T* __restrict__ out, const T* __restrict__ x,
                                  int D, float eps, size_t ldx, size_t ldo) {
     extern __shared__ float row[];
     __shared__ float scratch[33];
+    grid_dep_launch();
     const T* src = x + (size_t)blockIdx.x * ldx;
     T* dst = out + (size_t)blockIdx.x * ldo;
     float s = 0.f;
@@ -95,11 +96,97 @@ __global__ void layernorm_kernel(T* __restrict__ out, const T* __restrict__ x,
     }
 }
 
+// Eight consecutive elements of a weight or bias vector stored as float32 or bfloat16 (c a multiple of 8).
+__device__ __forceinline__ void load8_as_f32(const void* p, int dtype, int c, float (&f)[8]) {
+    if (dtype == QS_F32) {
+        const float4 a = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + c)[0];
+        const float4 b = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + c)[1];
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + c);
+        const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(u[j] << 16); f[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
+    }
+}
+
+// The same for bfloat16 rows whose width is a multiple of 8: one warp per row, the row kept in
+// registers as NV 16-byte pieces per lane (width <= 256 * NV), statistics by warp butterflies.
+template <int NV>
+__global__ void __launch_bounds__(128)
+layernorm_warp_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
+                      const void* __restrict__ w, int w_dtype, const void* __restrict__ b, int b_dtype,
+                      int rows, int D, float eps, size_t ldx, size_t ldo) {
+    grid_dep_launch();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const __nv_bfloat16* src = x + (size_t)row * ldx;
+    float v[NV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * 8;
+        if (c < D) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + c);
+            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { v[i][2 * j] = __uint_as_float(u[j] << 16); v[i][2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s += v[i][j];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+        }
+    }
+    const float mean = warp_sum(s) / (float)D;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if ((i * 32 + lane) * 8 < D) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; q += d * d; }
+        }
+    const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)D + eps);
+    __nv_bfloat16* dst = out + (size_t)row * ldo;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (i * 32 + lane) * 8;
+        if (c < D) {
+            uint32_t o[4];
+            float wf[8], bf[8];
+            load8_as_f32(w, w_dtype, c, wf);
+            if (b) load8_as_f32(b, b_dtype, c, bf);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float y0 = (v[i][2 * j] - mean) * rstd * wf[2 * j];
+                float y1 = (v[i][2 * j + 1] - mean) * rstd * wf[2 * j + 1];
+                if (b) { y0 += bf[2 * j]; y1 += bf[2 * j + 1]; }
+                const __nv_bfloat162 pb = __floats2bfloat162_rn(y0, y1);
+                o[j] = *reinterpret_cast<const uint32_t*>(&pb);
+            }
+            *reinterpret_cast<uint4*>(dst + c) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 QS_API int qs_layernorm(void* out, const void* x, int dtype, const void* w, int w_dtype,
                         const void* b, int b_dtype, int rows, int D, float eps,
                         long long ldx, long long ldo, cudaStream_t stream) {
     if (rows == 0) return QS_OK;
     QS_REQUIRE(rows > 0 && D > 0, "layernorm: bad sizes rows=%d D=%d", rows, D);
+    // many rows: one warp per row (few rows are served faster by a whole block per row, below)
+    if (dtype == QS_BF16 && rows >= 256 && D % 8 == 0 && D <= 4096 && ldx % 8 == 0 && ldo % 8 == 0 &&
+        ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)w % 16) == 0 && (!b || ((uintptr_t)b % 16) == 0)) {
+        const int nv = (D + 255) / 256;
+        const int warps = 4;
+        const int blocks = (rows + warps - 1) / warps;
+#define GO(NV) layernorm_warp_kernel<NV><<<blocks, warps * 32, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, \
+            w, w_dtype, b, b_dtype, rows, D, eps, (size_t)ldx, (size_t)ldo)
+        if (nv <= 1) GO(1); else if (nv <= 2) GO(2); else if (nv <= 4) GO(4); else if (nv <= 8) GO(8); else GO(16);
+#undef GO
+        return qs_check_launch("layernorm");
+    }
     const size_t smem = (size_t)D * sizeof(float);
     QS_REQUIRE(smem <= 200 * 1024, "layernorm: width %d does not fit one block's shared memory (max %d)",
                D, 200 * 1024 / 4);

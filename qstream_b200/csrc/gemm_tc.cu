@@ -6,12 +6,15 @@
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA issuer,
 // warps 2..5 = epilogue (warp w reads TMEM lanes 32 * (w % 4) .. +31).
 //
-// Two operand arrangements of the same kernel:
-//   rows of A on the MMA's M side (128 per tile), rows of W on its N side (BN per tile): many tokens;
-//   SWAP: rows of W on the M side, the few tokens of a decode step on the N side (BN = 16..64),
-//         so no tensor-core row is spent on padding and every CTA streams its own slab of W.
-// Each output element is accumulated over K in one TMEM cell in ascending k, so a row's result
-// does not depend on the other rows of the batch.
+// Two kernels:
+//   many tokens (M > 64): rows of A on the MMA's M side, rows of W on its N side; a persistent CTA per SM
+//       walks over 128 x 256 output tiles with two TMEM accumulators, so the epilogue of one tile runs
+//       under the main loop of the next;
+//   few tokens (M <= 64): rows of W on the M side and the tokens on the N side (16, 32 or 64), so no
+//       tensor-core row is spent on padding; one CTA per SM streams whole tiles of W, or - for a narrow
+//       N - an even share of all k-blocks (stream-K) with a deterministic reduction of partial tiles.
+// Each output element is accumulated over K in ascending k (in one TMEM cell, or in a fixed sequence of
+// partial sums), so a row's result does not depend on the other rows of the batch.
 //
 // Sizes: any M, N; K a multiple of 8 (TMA row pitch of 16 bytes); tails are zero-filled by TMA.
 #include "common.cuh"
@@ -28,10 +31,8 @@ constexpr int BM = 128;             // rows of the M-side operand per tile = TME
 constexpr int BK = 64;              // 64 bfloat16 = one 128-byte swizzled row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr int SMEM_BUDGET_BIG = 200 * 1024;     // many tokens: one CTA per SM, deep ring
-constexpr int SMEM_BUDGET_SWAP = 100 * 1024;    // few tokens: two CTAs per SM stream weights side by side
-constexpr int TARGET_CTAS = 2 * 148;            // CTAs resident at once in the weight-streaming arrangement
-constexpr int MIN_KB_PER_SPLIT = 8;             // k-blocks of 64 a split-K slice keeps at least
+constexpr int SMEM_BUDGET_BIG = 200 * 1024;     // one CTA per SM with a deep ring of stages
+constexpr int MIN_KB_PER_SPLIT = 8;             // k-blocks of 64 a CTA's share keeps at least
 
 struct Epilogue {
     void* C; int c_dtype; long long ldc;
@@ -41,10 +42,6 @@ struct Epilogue {
 };
 
 template <int BN> constexpr int stage_bytes() { return BM * BK * 2 + BN * BK * 2; }
-template <int BN, bool SWAP> constexpr int num_stages() {
-    return (SWAP ? SMEM_BUDGET_SWAP : SMEM_BUDGET_BIG) / stage_bytes<BN>();
-}
-template <int BN, bool SWAP> constexpr int smem_bytes() { return num_stages<BN, SWAP>() * stage_bytes<BN>() + 1024 + 256; }
 
 __device__ __forceinline__ void store_out(const Epilogue& ep, int m, int n, float v) {
     if (ep.bias) v += load_as_f32(ep.bias, ep.bias_dtype, n);
@@ -52,167 +49,6 @@ __device__ __forceinline__ void store_out(const Epilogue& ep, int m, int n, floa
     if (ep.res1) v += __bfloat162float(ep.res1[(size_t)m * ep.ldr + n]);
     if (ep.res2) v += __bfloat162float(ep.res2[(size_t)m * ep.ldr + n]);
     store_from_f32(ep.C, ep.c_dtype, (size_t)m * ep.ldc + n, v);
-}
-
-template <int BN, bool SWAP>
-__global__ void __launch_bounds__(THREADS, SWAP ? 2 : 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
-               const Epilogue ep, const int K, float* __restrict__ ws, int32_t* __restrict__ counters,
-               int32_t* __restrict__ status) {
-    constexpr int STAGES = num_stages<BN, SWAP>();
-    constexpr int STAGE = stage_bytes<BN>();
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-    constexpr int CH = BN < 32 ? 16 : 32;             // accumulator columns read per tcgen05.ld
-
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
-    volatile uint32_t* aborted = tmem_slot + 1;
-    volatile uint32_t* last_flag = tmem_slot + 2;
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int p0 = blockIdx.x * BM;                   // first row of the M-side operand
-    const int q0 = blockIdx.y * BN;                   // first row of the N-side operand
-    // split-K: CTA z of gridDim.z accumulates k-blocks [kb_begin, kb_end)
-    const int total_kb = (K + BK - 1) / BK;
-    const int splits = gridDim.z;
-    const int kb_begin = (int)((long long)blockIdx.z * total_kb / splits);
-    const int num_kb = (int)((long long)(blockIdx.z + 1) * total_kb / splits) - kb_begin;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
-        *aborted = 0;
-        mbar_fence_init();
-        prefetch_tensormap(&map_p);
-        prefetch_tensormap(&map_q);
-    }
-    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
-
-    if (warp == 0) {
-        if (elect_one()) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t phase = (kb / STAGES) & 1;
-                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 101); *aborted = 1; break; }
-                uint8_t* tile = smem + s * STAGE;
-                mbar_expect_tx(&full[s], STAGE);
-                tma_load_2d(tile, &map_p, &full[s], (kb_begin + kb) * BK, p0);
-                tma_load_2d(tile + BM * BK * 2, &map_q, &full[s], (kb_begin + kb) * BK, q0);
-            }
-        }
-    } else if (warp == 1) {
-        if (elect_one()) {
-            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
-            bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t phase = (kb / STAGES) & 1;
-                if (!mbar_wait(&full[s], phase)) { atomicExch(status, 102); *aborted = 1; ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t a_addr = smem_u32(smem + s * STAGE);
-                const uint64_t da = smem_desc_sw128(a_addr);
-                const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
-#pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 elements of K = 32 bytes = 2 units of the descriptor's address field
-                    mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-                }
-                mma_commit(&empty[s]);                // the stage is free once these MMAs have read it
-            }
-            mma_commit(acc_ready);                    // arrives even after a failed wait, so nobody hangs on it
-        }
-    } else {
-        const int quad = warp & 3;
-        bool ok = mbar_wait(acc_ready, 0);
-        if (!ok) atomicExch(status, 103);
-        ok = ok && *aborted == 0;
-        tc_fence_after_sync();
-        const int r = quad * 32 + lane;               // this thread's TMEM lane
-        const int p = p0 + r;                         // its row of the M-side operand
-        auto emit = [&](int c, const float (&v)[CH]) {
-            if constexpr (!SWAP) {
-                if (p < ep.M) {
-#pragma unroll
-                    for (int j = 0; j < CH; ++j) {
-                        const int n = q0 + c * CH + j;
-                        if (n < ep.N) store_out(ep, p, n, v[j]);
-                    }
-                }
-            } else {
-                if (p < ep.N) {
-#pragma unroll
-                    for (int j = 0; j < CH; ++j) {
-                        const int m = q0 + c * CH + j;
-                        if (m < ep.M) store_out(ep, m, p, v[j]);
-                    }
-                }
-            }
-        };
-        if (splits == 1) {
-            if (ok) {
-#pragma unroll 1
-                for (int c = 0; c < BN / CH; ++c) {
-                    uint32_t raw[CH];
-                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * CH);
-                    if constexpr (CH == 32) tmem_load_32x32(taddr, raw); else tmem_load_32x16(taddr, raw);
-                    tmem_load_wait();
-                    float v[CH];
-#pragma unroll
-                    for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(raw[j]);
-                    emit(c, v);
-                }
-            }
-        } else {
-            // Split-K: every slice leaves its 32-bit partial tile in the workspace; the CTA that arrives
-            // last adds the slices in slice order (its own included, read back like the others), so the
-            // sum does not depend on which CTA finished when.
-            const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
-            float* mine = ws + ((tile * splits + blockIdx.z) * BN) * BM;
-#pragma unroll 1
-            for (int c = 0; c < BN / CH; ++c) {
-                uint32_t raw[CH];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * CH);
-                if constexpr (CH == 32) tmem_load_32x32(taddr, raw); else tmem_load_32x16(taddr, raw);
-                tmem_load_wait();
-#pragma unroll
-                for (int j = 0; j < CH; ++j) mine[(size_t)(c * CH + j) * BM + r] = ok ? __uint_as_float(raw[j]) : 0.f;
-            }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps
-            if (threadIdx.x == 64) {
-                const int prev = atomicAdd(&counters[tile], 1);
-                *last_flag = (prev == splits - 1) ? 1u : 0u;
-                if (prev == splits - 1) counters[tile] = 0;           // ready for the next launch
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*last_flag) {
-                __threadfence();
-#pragma unroll 1
-                for (int c = 0; c < BN / CH; ++c) {
-                    float v[CH];
-#pragma unroll
-                    for (int j = 0; j < CH; ++j) v[j] = 0.f;
-                    for (int z = 0; z < splits; ++z) {
-                        const float* part = ws + ((tile * splits + z) * BN) * BM;
-#pragma unroll
-                        for (int j = 0; j < CH; ++j) v[j] += __ldcg(&part[(size_t)(c * CH + j) * BM + r]);
-                    }
-                    emit(c, v);
-                }
-            }
-        }
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // ----------------------------------------------------------------------------- persistent kernel (many tokens)
@@ -375,6 +211,201 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ----------------------------------------------------------------------------- stream-K kernel (few tokens)
+
+template <int BN> constexpr int s_stages() { return SMEM_BUDGET_BIG / stage_bytes<BN>(); }
+template <int BN> constexpr int s_smem_bytes() { return s_stages<BN>() * stage_bytes<BN>() + 1024 + 512; }
+
+// The CTA that holds work unit u when U units are dealt to G CTAs as [c U / G, (c + 1) U / G).
+__device__ __forceinline__ int owner_of(long long u, long long U, int G) { return (int)(((u + 1) * G - 1) / U); }
+
+// Decode-sized products (at most 64 tokens) are bound by the bytes of W.  Rows of W sit on the MMA's M
+// side (tiles of 128 output features), the tokens on its N side (BN = 16, 32 or 64).  The work - every
+// (tile, 64-wide k-block) pair, tile-major - is dealt in equal contiguous shares to gridDim.x CTAs, each
+// streaming its share through one uninterrupted TMA ring that fills the SM's shared memory.  When the
+// host picks gridDim.x = tiles, a share is exactly one tile and no partial sums exist.  A share may begin and end inside a tile: such partial sums go to a workspace slot of the
+// CTA, an arrival counter per tile tells the last contributor, and that CTA adds the partial tiles in
+// ascending k (ascending CTA) order and runs the epilogue.  No CTA ever waits for another.  The dealing
+// depends on N, K and the device only, so a token's result does not depend on its batch.
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                      const Epilogue ep, const int K, const int tiles, float* __restrict__ ws,
+                      int32_t* __restrict__ counters, int32_t* __restrict__ status) {
+    constexpr int STAGES = s_stages<BN>();
+    constexpr int STAGE = stage_bytes<BN>();
+    constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    constexpr int CH = BN < 32 ? 16 : 32;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;              // [2]
+    uint64_t* acc_empty = acc_full + 2;               // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* aborted = tmem_slot + 1;
+    volatile uint32_t* last_flag = tmem_slot + 2;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_kb = (K + BK - 1) / BK;
+    const long long U = (long long)tiles * total_kb;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const long long u_begin = (long long)cta * U / G, u_end = (long long)(cta + 1) * U / G;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
+        *aborted = 0;
+        mbar_fence_init();
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_a);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    grid_dep_launch();                                // the next kernel may be scheduled as CTAs of this one leave
+
+    if (warp == 0) {
+        if (elect_one()) {
+            // The weights are written by no kernel: the ring is filled with tiles of W right away, while the
+            // previous kernel may still be running; the tokens' tiles follow once it has completed.
+            const int ahead = (int)min((long long)STAGES, u_end - u_begin);
+            for (int i = 0; i < ahead; ++i) {
+                const long long u = u_begin + i;
+                const int tile = (int)(u / total_kb), kb = (int)(u - (long long)tile * total_kb);
+                mbar_expect_tx(&full[i], STAGE);
+                tma_load_2d(smem + i * STAGE, &map_w, &full[i], kb * BK, tile * BM);
+            }
+            grid_dep_wait();
+            for (int i = 0; i < ahead; ++i) {
+                const long long u = u_begin + i;
+                const int kb = (int)(u % total_kb);
+                tma_load_2d(smem + i * STAGE + BM * BK * 2, &map_a, &full[i], kb * BK, 0);
+            }
+            uint32_t it = ahead;
+            for (long long u = u_begin + ahead; u < u_end && !*aborted; ++u, ++it) {
+                const int tile = (int)(u / total_kb), kb = (int)(u - (long long)tile * total_kb);
+                const int s = it % STAGES;
+                if (!wait_or_abort(&empty[s], ((it / STAGES) & 1) ^ 1, aborted)) { atomicExch(status, 131); *aborted = 1; break; }
+                uint8_t* st = smem + s * STAGE;
+                mbar_expect_tx(&full[s], STAGE);
+                tma_load_2d(st, &map_w, &full[s], kb * BK, tile * BM);
+                tma_load_2d(st + BM * BK * 2, &map_a, &full[s], kb * BK, 0);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+            uint32_t it = 0;
+            int seg = 0;
+            for (long long u = u_begin; u < u_end && !*aborted; ++seg) {
+                const int tile = (int)(u / total_kb), kb0 = (int)(u - (long long)tile * total_kb);
+                const int n = (int)min((long long)(total_kb - kb0), u_end - u);
+                const int buf = seg & 1;
+                if (!wait_or_abort(&acc_empty[buf], ((seg >> 1) & 1) ^ 1, aborted)) { atomicExch(status, 132); *aborted = 1; break; }
+                tc_fence_after_sync();
+                for (int kb = 0; kb < n; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!wait_or_abort(&full[s], (it / STAGES) & 1, aborted)) { atomicExch(status, 133); *aborted = 1; break; }
+                    tc_fence_after_sync();
+                    const uint32_t w_addr = smem_u32(smem + s * STAGE);
+                    const uint64_t dw = smem_desc_sw128(w_addr);
+                    const uint64_t da = smem_desc_sw128(w_addr + BM * BK * 2);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        mma_bf16(tmem_base + (uint32_t)(buf * BN), dw + 2 * k, da + 2 * k, idesc, (kb | k) != 0);
+                    mma_commit(&empty[s]);
+                }
+                mma_commit(&acc_full[buf]);
+                u += n;
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;                   // TMEM lane = output feature within the tile
+        grid_dep_wait();                                  // residuals, outputs and the workspace belong to earlier kernels until now
+        int seg = 0;
+        for (long long u = u_begin; u < u_end; ++seg) {
+            const int tile = (int)(u / total_kb), kb0 = (int)(u - (long long)tile * total_kb);
+            const int n = (int)min((long long)(total_kb - kb0), u_end - u);
+            const int buf = seg & 1;
+            const int feat = tile * BM + r;
+            if (!wait_or_abort(&acc_full[buf], (seg >> 1) & 1, aborted)) { atomicExch(status, 134); *aborted = 1; break; }
+            tc_fence_after_sync();
+            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+            auto emit = [&](int c, const float (&v)[CH]) {
+                if (feat < ep.N) {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        const int m = c * CH + j;
+                        if (m < ep.M) store_out(ep, m, feat, v[j]);
+                    }
+                }
+            };
+            if (n == total_kb) {                          // the whole tile was accumulated here
+#pragma unroll 1
+                for (int c = 0; c < BN / CH; ++c) {
+                    uint32_t raw[CH];
+                    if constexpr (CH == 32) tmem_load_32x32(tacc + c * CH, raw); else tmem_load_32x16(tacc + c * CH, raw);
+                    tmem_load_wait();
+                    float v[CH];
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(raw[j]);
+                    emit(c, v);
+                }
+            } else {
+                // a CTA has at most two partial tiles: the one its share begins in (slot 0) and the one it ends in (slot 1)
+                float* mine = ws + ((size_t)cta * 2 + (seg == 0 ? 0 : 1)) * BN * BM;
+#pragma unroll 1
+                for (int c = 0; c < BN / CH; ++c) {
+                    uint32_t raw[CH];
+                    if constexpr (CH == 32) tmem_load_32x32(tacc + c * CH, raw); else tmem_load_32x16(tacc + c * CH, raw);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) mine[(size_t)(c * CH + j) * BM + r] = __uint_as_float(raw[j]);
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int c_first = owner_of((long long)tile * total_kb, U, G);
+                const int c_last = owner_of((long long)(tile + 1) * total_kb - 1, U, G);
+                if (threadIdx.x == 64) {
+                    const int prev = atomicAdd(&counters[tile], 1);
+                    const bool last = prev == c_last - c_first;
+                    *last_flag = last ? 1u : 0u;
+                    if (last) counters[tile] = 0;         // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+#pragma unroll 1
+                    for (int c = 0; c < BN / CH; ++c) {
+                        float v[CH];
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) v[j] = 0.f;
+                        for (int cc = c_first; cc <= c_last; ++cc) {
+                            const int first_tile = (int)(((long long)cc * U / G) / total_kb);
+                            const float* part = ws + ((size_t)cc * 2 + (first_tile == tile ? 0 : 1)) * BN * BM;
+#pragma unroll
+                            for (int j = 0; j < CH; ++j) v[j] += __ldcg(&part[(size_t)(c * CH + j) * BM + r]);
+                        }
+                        emit(c, v);
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");        // last_flag is read by all before it is reused
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&acc_empty[buf]);
+            u += n;
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 // ----------------------------------------------------------------------------- host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -436,30 +467,39 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
     return QS_OK;
 }
 
-// How many split-K slices the weight-streaming arrangement uses: a function of N and K only, never of
-// the number of tokens, so that a token's result does not depend on its batch.
-int choose_splits(int N, int K) {
-    const int tiles = (N + BM - 1) / BM;
-    const int total_kb = (K + BK - 1) / BK;
-    int splits = (TARGET_CTAS + tiles / 2) / tiles;
-    if (splits > total_kb / MIN_KB_PER_SPLIT) splits = total_kb / MIN_KB_PER_SPLIT;
-    return splits < 1 ? 1 : splits;
-}
-
-template <int BN, bool SWAP>
-int launch(const CUtensorMap& mp, const CUtensorMap& mq, const Epilogue& ep, int p_rows, int q_rows, int K,
-           int splits, float* ws, int32_t* counters, int32_t* status, cudaStream_t stream) {
+template <int BN>
+int launch_stream(const CUtensorMap& mw, const CUtensorMap& ma, const Epilogue& ep, int N, int K, float* ws,
+                  long long ws_floats, int32_t* counters, int n_counters, int32_t* status, cudaStream_t stream) {
     static bool configured = false;
+    static int sm_count = 0;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             smem_bytes<BN, SWAP>());
-        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc: shared memory of %d bytes refused: %s",
-                                             smem_bytes<BN, SWAP>(), cudaGetErrorString(e));
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_stream_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             s_smem_bytes<BN>());
+        int dev = 0;
+        if (e == cudaSuccess) e = cudaGetDevice(&dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc: set-up of the stream-K kernel failed: %s",
+                                             cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((p_rows + BM - 1) / BM, (q_rows + BN - 1) / BN, splits);
-    gemm_tc_kernel<BN, SWAP><<<grid, THREADS, smem_bytes<BN, SWAP>(), stream>>>(mp, mq, ep, K, ws, counters, status);
-    return qs_check_launch("gemm_tc");
+    const int tiles = (N + BM - 1) / BM;
+    const long long total_kb = (K + BK - 1) / BK;
+    const long long U = tiles * total_kb;
+    // One CTA per SM with a ring that fills its shared memory.  With enough tiles to occupy most SMs every
+    // CTA takes whole tiles (no partial sums at all); with fewer (a narrow N) the k-blocks are dealt evenly
+    // to one CTA per SM, in shares of at least MIN_KB_PER_SPLIT.  Both depend on N, K and the device only.
+    long long G = sm_count;
+    if (tiles * 5 >= (long long)sm_count * 3) G = tiles;
+    else {
+        if (G > U / MIN_KB_PER_SPLIT) G = U / MIN_KB_PER_SPLIT;
+        if (G < 1) G = 1;
+        if (!ws || !counters || tiles > n_counters || G * 2 * BN * BM > ws_floats) G = tiles;
+    }
+    QS_REQUIRE(tiles <= n_counters || !counters, "gemm_tc: %d tiles exceed the %d arrival counters", tiles, n_counters);
+    cudaError_t e = qs_launch_dependent(gemm_tc_stream_kernel<BN>, dim3((unsigned)G), dim3(THREADS), s_smem_bytes<BN>(), stream,
+                                        mw, ma, ep, K, tiles, ws, counters, status);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc stream: %s", cudaGetErrorString(e));
+    return qs_check_launch("gemm_tc stream");
 }
 
 template <int BN>
@@ -513,12 +553,9 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
         return launch_persistent<128>(ma, mw, ep, M, N, K, status, stream);
     }
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    int splits = choose_splits(N, K);
-    const long long tiles = (N + BM - 1) / BM;
-    if (!ws || !counters || tiles > n_counters || tiles * splits * 64 * BM > ws_floats) splits = 1;
     if ((rc = tensor_map(&mw, W, N, K, K, BM)) != QS_OK) return rc;
     if ((rc = tensor_map(&ma, A, M, K, lda, bn)) != QS_OK) return rc;
-    if (bn == 16) return launch<16, true>(mw, ma, ep, N, M, K, splits, ws, counters, status, stream);
-    if (bn == 32) return launch<32, true>(mw, ma, ep, N, M, K, splits, ws, counters, status, stream);
-    return launch<64, true>(mw, ma, ep, N, M, K, splits, ws, counters, status, stream);
+    if (bn == 16) return launch_stream<16>(mw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    if (bn == 32) return launch_stream<32>(mw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    return launch_stream<64>(mw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
 }
