@@ -26,6 +26,8 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
                                   T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   int32_t* __restrict__ status) {
     // blockIdx.x = token; the gridDim.y blocks of a token share its (head, pair of dims) items of q, then k and v
+    grid_dep_launch();
+    grid_dep_wait();
     const int t = blockIdx.x;
     const int tid = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
     const int slot = tok_slot[t];
@@ -211,11 +213,11 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
     if (T_tokens < 256) { per_token = (n_kv_heads * dh / 2 + threads - 1) / threads; if (per_token > 16) per_token = 16; if (per_token < 1) per_token = 1; }
     dim3 grid(T_tokens, per_token);
     if (dtype == QS_F32)
-        rope_store_kernel<float><<<grid, threads, 0, stream>>>((float*)q, (const float*)k, (const float*)v,
+        qs_launch_dependent(rope_store_kernel<float>, grid, dim3(threads), 0, stream, (float*)q, (const float*)k, (const float*)v,
             (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos,
             page_table, max_pages, shift, (float*)k_cache, (float*)v_cache, status);
     else if (dtype == QS_BF16)
-        rope_store_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)q, (const __nv_bfloat16*)k,
+        qs_launch_dependent(rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)q, (const __nv_bfloat16*)k,
             (const __nv_bfloat16*)v, (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos,
             tok_slot, tok_pos, page_table, max_pages, shift, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status);
     else return qs_fail(QS_ERR_INVALID_INPUT, "rope_store: unknown dtype %d", dtype);

@@ -73,6 +73,7 @@ __global__ void layernorm_kernel(T* __restrict__ out, const T* __restrict__ x,
     extern __shared__ float row[];
     __shared__ float scratch[33];
     grid_dep_launch();
+    grid_dep_wait();
     const T* src = x + (size_t)blockIdx.x * ldx;
     T* dst = out + (size_t)blockIdx.x * ldo;
     float s = 0.f;
@@ -118,6 +119,7 @@ layernorm_warp_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __re
                       const void* __restrict__ w, int w_dtype, const void* __restrict__ b, int b_dtype,
                       int rows, int D, float eps, size_t ldx, size_t ldo) {
     grid_dep_launch();
+    grid_dep_wait();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -181,8 +183,8 @@ QS_API int qs_layernorm(void* out, const void* x, int dtype, const void* w, int 
         const int nv = (D + 255) / 256;
         const int warps = 4;
         const int blocks = (rows + warps - 1) / warps;
-#define GO(NV) layernorm_warp_kernel<NV><<<blocks, warps * 32, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, \
-            w, w_dtype, b, b_dtype, rows, D, eps, (size_t)ldx, (size_t)ldo)
+#define GO(NV) qs_launch_dependent(layernorm_warp_kernel<NV>, dim3(blocks), dim3(warps * 32), 0, stream, (__nv_bfloat16*)out, \
+            (const __nv_bfloat16*)x, w, w_dtype, b, b_dtype, rows, D, eps, (size_t)ldx, (size_t)ldo)
         if (nv <= 1) GO(1); else if (nv <= 2) GO(2); else if (nv <= 4) GO(4); else if (nv <= 8) GO(8); else GO(16);
 #undef GO
         return qs_check_launch("layernorm");
@@ -195,11 +197,11 @@ QS_API int qs_layernorm(void* out, const void* x, int dtype, const void* w, int 
     cudaError_t e = cudaSuccess;
     if (dtype == QS_F32) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess) layernorm_kernel<float><<<rows, threads, smem, stream>>>(
+        if (e == cudaSuccess) e = qs_launch_dependent(layernorm_kernel<float>, dim3(rows), dim3(threads), smem, stream,
             (float*)out, (const float*)x, w, w_dtype, b, b_dtype, D, eps, (size_t)ldx, (size_t)ldo);
     } else if (dtype == QS_BF16) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e == cudaSuccess) layernorm_kernel<__nv_bfloat16><<<rows, threads, smem, stream>>>(
+        if (e == cudaSuccess) e = qs_launch_dependent(layernorm_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), smem, stream,
             (__nv_bfloat16*)out, (const __nv_bfloat16*)x, w, w_dtype, b, b_dtype, D, eps, (size_t)ldx, (size_t)ldo);
     } else {
         return qs_fail(QS_ERR_INVALID_INPUT, "layernorm: unknown dtype %d", dtype);
