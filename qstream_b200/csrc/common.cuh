@@ -108,12 +108,28 @@ __device__ __forceinline__ float gelu_tanh(float v) {
     return 0.5f * v * (1.0f + tanhf(c * (v + 0.044715f * v * v * v)));
 }
 
+// The same function with tanh(u) = 1 - 2 / (exp(2u) + 1) on the fast exponential: a handful of
+// instructions instead of tanhf's forty, absolute error below 1e-6.  For epilogues that must keep up
+// with the tensor cores; the float32 engine uses gelu_tanh.
+__device__ __forceinline__ float gelu_tanh_fast(float v) {
+    const float c = 0.7978845608028654f;
+    const float u = c * (v + 0.044715f * v * v * v);
+    const float t = 1.0f - __fdividef(2.0f, __expf(2.0f * u) + 1.0f);
+    return 0.5f * v * (1.0f + t);
+}
+
 __device__ __forceinline__ float gelu_erf(float v) {
     return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
 }
 
 __device__ __forceinline__ float apply_activation(float v, int act) {
     if (act == QS_ACT_GELU_TANH) return gelu_tanh(v);
+    if (act == QS_ACT_GELU_ERF) return gelu_erf(v);
+    return v;
+}
+
+__device__ __forceinline__ float apply_activation_fast(float v, int act) {
+    if (act == QS_ACT_GELU_TANH) return gelu_tanh_fast(v);
     if (act == QS_ACT_GELU_ERF) return gelu_erf(v);
     return v;
 }

@@ -45,7 +45,7 @@ template <int BN> constexpr int stage_bytes() { return BM * BK * 2 + BN * BK * 2
 
 __device__ __forceinline__ void store_out(const Epilogue& ep, int m, int n, float v) {
     if (ep.bias) v += load_as_f32(ep.bias, ep.bias_dtype, n);
-    v = apply_activation(v, ep.act);
+    v = apply_activation_fast(v, ep.act);
     if (ep.res1) v += __bfloat162float(ep.res1[(size_t)m * ep.ldr + n]);
     if (ep.res2) v += __bfloat162float(ep.res2[(size_t)m * ep.ldr + n]);
     store_from_f32(ep.C, ep.c_dtype, (size_t)m * ep.ldc + n, v);
@@ -174,7 +174,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                         for (int j = 0; j < 8; ++j) {
                             float x = __uint_as_float(raw[g * 8 + j]);
                             if (ep.bias) x += load_as_f32(ep.bias, ep.bias_dtype, nc + g * 8 + j);
-                            v[j] = apply_activation(x, ep.act);
+                            v[j] = apply_activation_fast(x, ep.act);
                         }
                         if (ep.res1) {
                             const uint4 rr = *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + nc + g * 8);
