@@ -18,18 +18,7 @@ def _bind():
         _scratch_size = ops.bind("qs_attention_decode_scratch", [c_int, c_int, c_int, c_int], c_longlong)
         _decode = ops.bind("qs_attention_decode", [
             c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
-            c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
-
-
-_counters = {}
-
-
-def decode_counters(device) -> torch.Tensor:
-    """Zeroed arrival counters of the splits, one per (token, head); the kernel leaves them zero."""
-    key = (device.type, device.index)
-    if key not in _counters:
-        _counters[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
-    return _counters[key]
+            c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
 
 
 def decode(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table, page_tokens,
@@ -40,14 +29,11 @@ def decode(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, p
     out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     n = _scratch_size(T, n_heads, head_dim, max_context)
     scratch = torch.empty((n,), dtype=torch.float32, device=q.device)
-    counters = decode_counters(q.device)
-    if T * n_heads > counters.numel():
-        from ..errors import QsError, QStreamError
-        raise QStreamError(QsError.INVALID_INPUT, f"decode attention: {T} tokens x {n_heads} heads exceed its counters")
     ops.check(_decode(ops.ptr(out), out.stride(0), ops.ptr(q), q.stride(0), ops.ptr(k_cache), ops.ptr(v_cache),
                       ops.ptr(page_table), page_table.shape[1], page_tokens, ops.ptr(tok_slot), ops.ptr(tok_pos),
                       T, n_heads, n_kv_heads, head_dim, float(scale), int(window), int(max_context),
-                      ops.ptr(scratch), ops.ptr(counters), ops.ptr(status), ops.stream()))
+                      ops.ptr(scratch), ops.ptr(status), ops.stream()))
+    ops.count_launches(1)                                   # split kernel + merge kernel
     return out
 
 

@@ -1,6 +1,5 @@
 // Decode attention for bfloat16: one query token per sequence against its paged cache, with the
-// keys cut into splits of 256 (four pages of 64) that run as separate CTAs; the split that finishes
-// last merges the row.
+// keys cut into splits of 256 (four pages of 64) that run as separate CTAs, and a merge kernel.
 //
 // The kernel is bound by the bytes of K and V it streams (one multiply-add per byte and head),
 // so it runs on the CUDA cores with 16-byte loads; scores, maxima, exponentials, sums and the
@@ -34,8 +33,7 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float (&f)[8]) {
 // handled per warp instruction.
 template <int NCH>
 __global__ void __launch_bounds__(WARPS * 32)
-decode_split_kernel(__nv_bfloat16* __restrict__ out_rows, size_t ldo, float* __restrict__ partial,
-                    int32_t* __restrict__ counters, const __nv_bfloat16* __restrict__ q, size_t ldq,
+decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict__ q, size_t ldq,
                     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                     const int32_t* __restrict__ page_table, int max_pages,
                     const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
@@ -43,19 +41,11 @@ decode_split_kernel(__nv_bfloat16* __restrict__ out_rows, size_t ldo, float* __r
                     int32_t* __restrict__ status) {
     __shared__ float s_scores[WARPS][PAGE];
     __shared__ float s_m[WARPS], s_l[WARPS];
-    __shared__ int s_last;
     extern __shared__ float s_acc[];                 // [WARPS][dh]
 
-    grid_dep_launch();
-    grid_dep_wait();
     const int split = blockIdx.x, head = blockIdx.y, t = blockIdx.z;
     const int slot = tok_slot[t];
-    if (slot < 0) {                                   // padding: a defined output, written by the row's first split
-        if (split == 0)
-            for (int d = threadIdx.x; d < dh; d += blockDim.x)
-                out_rows[(size_t)t * ldo + (size_t)head * dh + d] = __float2bfloat16_rn(0.f);
-        return;
-    }
+    if (slot < 0) return;
     const int pos = tok_pos[t];
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
     if (split * SPLIT > pos || (split + 1) * SPLIT <= first) return;       // no visible key in this split
@@ -204,43 +194,44 @@ decode_split_kernel(__nv_bfloat16* __restrict__ out_rows, size_t ldo, float* __r
         out[dh] = M;
         out[dh + 1] = L;
     }
-    // The split that arrives last adds all of the row's splits in ascending split order, so the result
-    // does not depend on which finished when.  No split waits for another.
-    const int s_lo = first / SPLIT, s_hi = pos / SPLIT;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int32_t* counter = counters + (size_t)t * n_heads + head;
-        const int prev = atomicAdd(counter, 1);
-        s_last = prev == s_hi - s_lo;
-        if (s_last) *counter = 0;                     // ready for the next launch
+}
+
+// One block per (token, head): add the splits' partial results in ascending split order.
+__global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo, const float* __restrict__ partial,
+                                    const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                                    int n_heads, int dh, int window, int max_splits) {
+    grid_dep_launch();
+    const int head = blockIdx.x, t = blockIdx.y;
+    __nv_bfloat16* o = out + (size_t)t * ldo + (size_t)head * dh;
+    if (tok_slot[t] < 0) {
+        for (int d = threadIdx.x; d < dh; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+        return;
     }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
+    const int pos = tok_pos[t];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int s_lo = first / SPLIT, s_hi = pos / SPLIT;
     const float* base = partial + ((size_t)t * n_heads + head) * max_splits * (dh + 2);
-    float Mx = -INFINITY;
-    for (int sp = s_lo; sp <= s_hi; ++sp) Mx = fmaxf(Mx, __ldcg(&base[(size_t)sp * (dh + 2) + dh]));
+    float M = -INFINITY;
+    for (int s = s_lo; s <= s_hi; ++s) M = fmaxf(M, base[(size_t)s * (dh + 2) + dh]);
     float L = 0.f;
-    for (int sp = s_lo; sp <= s_hi; ++sp) {
-        const float ms = __ldcg(&base[(size_t)sp * (dh + 2) + dh]);
-        if (ms != -INFINITY) L += __ldcg(&base[(size_t)sp * (dh + 2) + dh + 1]) * expf(ms - Mx);
+    for (int s = s_lo; s <= s_hi; ++s) {
+        const float ms = base[(size_t)s * (dh + 2) + dh];
+        if (ms != -INFINITY) L += base[(size_t)s * (dh + 2) + dh + 1] * expf(ms - M);
     }
     const float inv = L > 0.f ? 1.0f / L : 0.f;
-    __nv_bfloat16* o = out_rows + (size_t)t * ldo + (size_t)head * dh;
     for (int d = threadIdx.x; d < dh; d += blockDim.x) {
-        float acc_d = 0.f;
-        for (int sp = s_lo; sp <= s_hi; ++sp) {
-            const float ms = __ldcg(&base[(size_t)sp * (dh + 2) + dh]);
-            if (ms != -INFINITY) acc_d += __ldcg(&base[(size_t)sp * (dh + 2) + d]) * expf(ms - Mx);
+        float acc = 0.f;
+        for (int s = s_lo; s <= s_hi; ++s) {
+            const float ms = base[(size_t)s * (dh + 2) + dh];
+            if (ms != -INFINITY) acc += base[(size_t)s * (dh + 2) + d] * expf(ms - M);
         }
-        o[d] = __float2bfloat16_rn(acc_d * inv);
+        o[d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
 }  // namespace
 
-// How many floats of scratch `qs_attention_decode` needs for the splits' partial results.
+// How many floats of scratch `qs_attention_decode` needs.
 QS_API long long qs_attention_decode_scratch(int T_tokens, int n_heads, int dh, int max_context) {
     const long long max_splits = (max_context + SPLIT - 1) / SPLIT;
     return (long long)T_tokens * n_heads * max_splits * (dh + 2);
@@ -249,13 +240,12 @@ QS_API long long qs_attention_decode_scratch(int T_tokens, int n_heads, int dh, 
 // out [T, n_heads * dh] bfloat16.  One query token per row; `max_context` bounds every row's
 // position + 1 and fixes the grid, so the same launch serves every length (CUDA graphs).
 // `scratch`: float32, at least qs_attention_decode_scratch(...) elements; contents need no
-// initialisation.  `counters`: T_tokens * n_heads int32 that are ZERO before the first call; the
-// kernel leaves them zero.  Calls that share scratch or counters must not overlap on the GPU.
+// initialisation.
 QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
                                const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
                                const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
                                int n_kv_heads, int dh, float scale, int window, int max_context,
-                               float* scratch, int32_t* counters, int32_t* status, cudaStream_t stream) {
+                               float* scratch, int32_t* status, cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
     QS_REQUIRE(T_tokens > 0 && n_heads > 0 && n_kv_heads > 0 && dh > 0 && max_context > 0, "attention_decode: bad sizes");
     QS_REQUIRE(page_tokens == PAGE, "attention_decode: pages of %d tokens, the kernel is built for %d", page_tokens, PAGE);
@@ -270,13 +260,16 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
     const int nch = (n_chunks + 31) / 32;
     dim3 grid(max_splits, n_heads, T_tokens);
     const size_t smem = (size_t)WARPS * dh * sizeof(float);
-#define GO(NCH) qs_launch_dependent(decode_split_kernel<NCH>, grid, dim3(WARPS * 32), smem, stream, \
-        (__nv_bfloat16*)out, (size_t)ldo, scratch, counters, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, \
-        (const __nv_bfloat16*)v_cache, \
+#define GO(NCH) decode_split_kernel<NCH><<<grid, WARPS * 32, smem, stream>>>( \
+        scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
         page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, max_splits, status)
     if (nch == 1) GO(1); else GO(2);
 #undef GO
-    return qs_check_launch("attention_decode");
+    int rc = qs_check_launch("attention_decode");
+    if (rc != QS_OK) return rc;
+    decode_merge_kernel<<<dim3(n_heads, T_tokens), dh >= 128 ? 128 : 64, 0, stream>>>(
+        (__nv_bfloat16*)out, (size_t)ldo, scratch, tok_slot, tok_pos, n_heads, dh, window, max_splits);
+    return qs_check_launch("attention_decode merge");
 }
 
 // ----------------------------------------------------------------------------- no allocation
@@ -288,13 +281,10 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
 
 // In host code this name is only a handle for cudaGetSymbolAddress, not a device address.
 static __device__ __align__(256) float g_decode_static_scratch[QS_DECODE_STATIC_SCRATCH_FLOATS];
-// Arrival counters of the splits, one per (token, head); zero at load time and left zero by every call.
-static __device__ __align__(256) int32_t g_decode_static_counters[QS_DECODE_STATIC_COUNTERS];
 
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_decode_static_ptr[kMaxDevices] = {nullptr};
-int32_t* g_decode_static_counters_ptr[kMaxDevices] = {nullptr};
 }  // namespace
 
 QS_API int qs_attention_decode_static(void* out, long long ldo, const void* q, long long ldq,
@@ -309,9 +299,6 @@ QS_API int qs_attention_decode_static(void* out, long long ldo, const void* q, l
     QS_REQUIRE(need <= (long long)QS_DECODE_STATIC_SCRATCH_FLOATS,
                "attention_decode_static: the call needs %lld floats of scratch, the built-in array holds %d "
                "(tokens * heads * ceil(context / 256) * (head size + 2))", need, QS_DECODE_STATIC_SCRATCH_FLOATS);
-    QS_REQUIRE((long long)T_tokens * n_heads <= (long long)QS_DECODE_STATIC_COUNTERS,
-               "attention_decode_static: %d tokens x %d heads exceed the %d built-in counters", T_tokens, n_heads,
-               QS_DECODE_STATIC_COUNTERS);
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
@@ -321,14 +308,9 @@ QS_API int qs_attention_decode_static(void* out, long long ldo, const void* q, l
         e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
         if (e != cudaSuccess || !p)
             return qs_fail(QS_ERR_INTERNAL, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        int32_t* c = nullptr;
-        e = cudaGetSymbolAddress((void**)&c, g_decode_static_counters);
-        if (e != cudaSuccess || !c)
-            return qs_fail(QS_ERR_INTERNAL, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        g_decode_static_counters_ptr[device] = c;
         g_decode_static_ptr[device] = p;
     }
     return qs_attention_decode(out, ldo, q, ldq, k_cache, v_cache, page_table, max_pages, page_tokens, tok_slot,
                                tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window, max_context,
-                               g_decode_static_ptr[device], g_decode_static_counters_ptr[device], status, stream);
+                               g_decode_static_ptr[device], status, stream);
 }

@@ -17,17 +17,14 @@
  *  - Limit: the scratch holds QS_DECODE_STATIC_SCRATCH_FLOATS floats (4 MiB).  A call needs
  *    T_tokens * n_heads * ceil(max_context / 256) * (head_dim + 2) floats; a larger call is
  *    refused with QS_ERR_INVALID_INPUT (11) and a message in qs_last_error(), nothing runs.
- *    The same holds for more than QS_DECODE_STATIC_COUNTERS (16,384) token-head pairs, each of which
- *    has an arrival counter (64 KiB in all) beside the scratch.
  *  - Cost: every GPU that loads the library holds these 4 MiB until the process exits.
  *  - First call on a device: the library looks up the array's device address once per
  *    device (cudaGetSymbolAddress, with that device current) and remembers it.  Make the
  *    first call on each device outside any stream capture.
  *  - The function calls no cudaMalloc, cudaFree or other allocating routine.
  *  - Sharing: all calls on a device use the same array, which keeps what the last call
- *    left in it.  Nothing in the scratch has to start at zero (every element that is read has been
- *    written earlier in the same call), so nothing is cleared; the counters start at zero when the
- *    library is loaded and every call hands them back at zero.  Two calls whose kernels may
+ *    left in it.  Nothing in it has to start at zero (every element that is read has been
+ *    written earlier in the same call), so nothing is cleared.  Two calls whose kernels may
  *    overlap on the GPU (different streams, no ordering between them) race on the array and
  *    give wrong results; calls on one stream, or ordered by events, are safe.
  *
@@ -44,7 +41,6 @@ extern "C" {
 #endif
 
 #define QS_DECODE_STATIC_SCRATCH_FLOATS (1 << 20)
-#define QS_DECODE_STATIC_COUNTERS (1 << 14)
 
 int qs_attention_decode_static(void* out, long long ldo, const void* q, long long ldq,
                                const void* k_cache, const void* v_cache,

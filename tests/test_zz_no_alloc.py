@@ -26,7 +26,7 @@ def _library():
     lib = ctypes.CDLL(str(build.build()))
     lib.qs_attention_decode_static.argtypes = ARGS + [c_void_p, c_void_p]
     lib.qs_attention_decode_static.restype = c_int
-    lib.qs_attention_decode.argtypes = ARGS + [c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.qs_attention_decode.argtypes = ARGS + [c_void_p, c_void_p, c_void_p]
     lib.qs_attention_decode.restype = c_int
     lib.qs_attention_decode_scratch.argtypes = [c_int, c_int, c_int, c_int]
     lib.qs_attention_decode_scratch.restype = c_longlong
@@ -62,9 +62,7 @@ def test_static_scratch_matches_caller_scratch_twice():
                   slot.data_ptr(), pos.data_ptr(), T, H, H, dh, dh ** -0.5, 0, ctx]
         want = torch.empty(T, H * dh, dtype=torch.bfloat16).cuda()
         scratch = torch.empty(lib.qs_attention_decode_scratch(T, H, dh, ctx), dtype=torch.float32).cuda()
-        counters = torch.zeros(T * H, dtype=torch.int32).cuda()
-        rc = lib.qs_attention_decode(want.data_ptr(), H * dh, *common, scratch.data_ptr(), counters.data_ptr(),
-                                     status.data_ptr(), stream)
+        rc = lib.qs_attention_decode(want.data_ptr(), H * dh, *common, scratch.data_ptr(), status.data_ptr(), stream)
         assert rc == 0, lib.qs_last_error()
         got = torch.full((T, H * dh), float("nan"), dtype=torch.bfloat16).cuda()
         rc = lib.qs_attention_decode_static(got.data_ptr(), H * dh, *common, status.data_ptr(), stream)
