@@ -22,11 +22,12 @@ def _bind():
 
 
 def decode(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table, page_tokens,
-           k_cache, v_cache, max_context, status) -> torch.Tensor:
+           k_cache, v_cache, max_context, status, out=None) -> torch.Tensor:
     """One query token per row against the paged cache, split over the keys and merged."""
     _bind()
     T = q.shape[0]
-    out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    if out is None:
+        out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     n = _scratch_size(T, n_heads, head_dim, max_context)
     scratch = torch.empty((n,), dtype=torch.float32, device=q.device)
     ops.check(_decode(ops.ptr(out), out.stride(0), ops.ptr(q), q.stride(0), ops.ptr(k_cache), ops.ptr(v_cache),
@@ -56,7 +57,7 @@ def prefill_tiles(batch, device) -> torch.Tensor:
 
 
 def prefill(q, n_heads, n_kv_heads, head_dim, scale, window, tiles, page_table, page_tokens, k_cache, v_cache,
-            status, padded=False) -> torch.Tensor:
+            status, padded=False, out=None) -> torch.Tensor:
     """Many query rows per sequence against the paged cache on the tensor cores (tcgen05)."""
     global _prefill
     if _prefill is None:
@@ -65,7 +66,10 @@ def prefill(q, n_heads, n_kv_heads, head_dim, scale, window, tiles, page_table, 
             c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
     T = q.shape[0]
     # rows that belong to no sequence (padding) are covered by no tile: give them a defined value
-    out = (torch.zeros if padded else torch.empty)((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    if out is None:
+        out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    if padded:
+        out.zero_()
     ops.check(_prefill(ops.ptr(out), out.stride(0), ops.ptr(q), q.stride(0), T, ops.ptr(k_cache), ops.ptr(v_cache),
                        k_cache.shape[0], ops.ptr(page_table), page_table.shape[1], page_tokens, ops.ptr(tiles),
                        tiles.shape[0], n_heads, n_kv_heads, head_dim, float(scale), int(window), ops.ptr(status),
@@ -73,18 +77,18 @@ def prefill(q, n_heads, n_kv_heads, head_dim, scale, window, tiles, page_table, 
     return out
 
 
-def attend(q, spec, step, view):
+def attend(q, spec, step, view, out=None):
     """The specialised kernel's output, or None if the generic kernel is to run."""
     b = step.batch
     if (b.decode and view.page_tokens == 64 and spec.head_dim % 8 == 0 and spec.head_dim <= 512
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
         return decode(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window, b.tok_slot,
                       b.tok_pos, view.page_table, view.page_tokens, view.k, view.v, step.cache.max_context,
-                      step.status)
+                      step.status, out=out)
     if (not b.decode and b.slots and view.page_tokens == 64 and spec.head_dim % 16 == 0 and spec.head_dim <= 256
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
         tiles = prefill_tiles(b, q.device)
         return prefill(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window, tiles,
                        view.page_table, view.page_tokens, view.k, view.v, step.status,
-                       padded=b.n_tokens != sum(b.new_tokens))
+                       padded=b.n_tokens != sum(b.new_tokens), out=out)
     return None

@@ -58,12 +58,15 @@ def takes(x, weight) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None) -> torch.Tensor:
+def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, out=None) -> torch.Tensor:
     M, K = x.shape
     N, K2 = weight.shape
     if K2 != K:
         raise QStreamError(QsError.INVALID_INPUT, f"linear: x is [{M}, {K}] but weight is {tuple(weight.shape)}")
-    out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
+    elif out.shape != (M, N) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise QStreamError(QsError.INVALID_INPUT, "linear: the output view does not fit")
     res = [r for r in residuals if r is not None]
     if len(res) > 2:
         raise QStreamError(QsError.INVALID_INPUT, "linear: at most two residuals")
@@ -78,7 +81,7 @@ def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None) 
     ws, counters = scratch(x.device)
     ops.check(_entry()(ops.ptr(out), ops.dtype_code(out), ops.ptr(x), ops.ptr(weight), ops.ptr(bias),
                        ops.dtype_code(bias) if bias is not None else 0, ops.ACTIVATIONS[activation],
-                       ops.ptr(res[0]), ops.ptr(res[1]), M, N, K, x.stride(0), N, ldr,
+                       ops.ptr(res[0]), ops.ptr(res[1]), M, N, K, x.stride(0), out.stride(0), ldr,
                        ops.ptr(ws), ws.numel(), ops.ptr(counters), counters.numel(),
                        ops.ptr(status_word(x.device)), ops.stream()))
     return out

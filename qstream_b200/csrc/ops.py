@@ -177,13 +177,16 @@ def add(a: torch.Tensor, b: torch.Tensor, c=None) -> torch.Tensor:
     return out
 
 
-def linear_simt(x, weight, bias=None, activation=None, residuals=(), out_dtype=None) -> torch.Tensor:
+def linear_simt(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, out=None) -> torch.Tensor:
     """act(x W^T + bias) + residuals, accumulated in true 32-bit on the CUDA cores."""
     M, K, lda = _rows(x)
     N, K2 = weight.shape
     if K2 != K or not weight.is_contiguous():
         raise QStreamError(QsError.INVALID_INPUT, f"linear: x is [{M}, {K}] but weight is {tuple(weight.shape)}")
-    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    elif out.shape != (M, N) or out.stride(1) != 1:
+        raise QStreamError(QsError.INVALID_INPUT, "linear: the output view does not fit")
     res = list(residuals) + [None, None]
     ldr = N
     for r in res[:2]:
@@ -195,7 +198,7 @@ def linear_simt(x, weight, bias=None, activation=None, residuals=(), out_dtype=N
         raise QStreamError(QsError.INVALID_INPUT, "linear: at most two residuals of one layout")
     check(library().qs_linear_simt(ptr(out), dtype_code(out), ptr(x), dtype_code(x), ptr(weight),
                                    dtype_code(weight), ptr(bias), dtype_code(bias) if bias is not None else 0,
-                                   ACTIVATIONS[activation], ptr(res[0]), ptr(res[1]), M, N, K, lda, N, ldr,
+                                   ACTIVATIONS[activation], ptr(res[0]), ptr(res[1]), M, N, K, lda, out.stride(0), ldr,
                                    stream()))
     return out
 
@@ -217,10 +220,11 @@ def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_
 
 
 def attention(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table,
-              page_tokens, k_cache, v_cache, status) -> torch.Tensor:
+              page_tokens, k_cache, v_cache, status, out=None) -> torch.Tensor:
     """Causal attention of every token over its sequence's cache (generic kernel)."""
     T = q.shape[0]
-    out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
     check(library().qs_attention(
         ptr(out), ptr(q), dtype_code(q), out.stride(0), q.stride(0), ptr(k_cache), ptr(v_cache),
         _int32(page_table, "page_table"), page_table.shape[1], page_tokens, _int32(tok_slot, "tok_slot"),

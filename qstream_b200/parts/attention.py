@@ -64,6 +64,16 @@ class Attention(Mixer):
         return KvNeed(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
 
     def forward(self, h, step, cache_id, residuals=()):
+        o = self.forward_hidden(h, step, cache_id)
+        return linear(o, self.w_out, self.b_out, residuals=residuals)
+
+    # A parallel block may fuse this part's output projection with the feed-forward's down projection:
+    # it takes the projection from `output_projection()` and calls `forward_hidden` with a view to fill.
+    def output_projection(self):
+        return self.w_out, self.b_out
+
+    def forward_hidden(self, h, step, cache_id, out=None):
+        """Everything before the output projection: [T, n_heads * head_dim], written to `out` if given."""
         s = self.spec
         b = step.batch
         view = step.kv(cache_id)
@@ -88,22 +98,21 @@ class Attention(Mixer):
                            self.position.rotary_dim if table is not None else 0, table,
                            b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
                            step.status)
-        o = attend(q, s, step, view)
-        return linear(o, self.w_out, self.b_out, residuals=residuals)
+        return attend(q, s, step, view, out)
 
 
-def attend(q, spec, step, view):
+def attend(q, spec, step, view, out=None):
     """Pick the attention kernel for this step: decode and prefill have their own
     bfloat16 kernels; the generic kernel takes every other case."""
     b = step.batch
     if q.dtype == torch.bfloat16:
         from ..csrc import attention_bf16
-        out = attention_bf16.attend(q, spec, step, view)
-        if out is not None:
-            return out
+        done = attention_bf16.attend(q, spec, step, view, out)
+        if done is not None:
+            return done
     return ops.attention(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window,
                          b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
-                         step.status)
+                         step.status, out=out)
 
 
 register("mixer", "attention", Attention)

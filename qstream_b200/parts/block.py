@@ -32,12 +32,40 @@ class Arrangement(Part):
 
 
 class ParallelBlock(Arrangement):
+    """x + mixer(h) + ffn(h).  When both parts end in a projection to the width (they offer
+    `output_projection()` and `forward_hidden(..., out=view)`) and the weights are bfloat16, the two
+    projections become one matrix product over the concatenated hidden vectors:
+    x + [o | g] [W_o | W_down]^T + (b_o + b_down), with the residual added on its 32-bit accumulator."""
     norm_names = ("input",)
+
+    def __init__(self, spec, parts, runtime):
+        super().__init__(spec, parts, runtime)
+        self.fused_weight = None
+        import torch
+        fusable = all(hasattr(p, "output_projection") and hasattr(p, "forward_hidden") for p in (self.mixer, self.ffn))
+        if fusable and runtime.dtype == torch.bfloat16:
+            (wm, bm), (wf, bf) = self.mixer.output_projection(), self.ffn.output_projection()
+            if (wm.dtype == wf.dtype == torch.bfloat16 and wm.shape[0] == wf.shape[0]
+                    and wm.shape[1] % 8 == 0 and wf.shape[1] % 8 == 0):
+                self.k_mixer = wm.shape[1]
+                self.fused_weight = torch.cat([wm, wf], dim=1).contiguous()
+                biases = [b.float() for b in (bm, bf) if b is not None]
+                self.fused_bias = sum(biases[1:], biases[0]) if biases else None
+                # the parts keep views of the fused matrix, so the weights are held once
+                self.mixer.w_out = self.fused_weight[:, :self.k_mixer]
+                self.ffn.down = self.fused_weight[:, self.k_mixer:]
 
     def forward(self, x, step, cache_id):
         h = self.norms["input"].forward(x)
-        a = self.mixer.forward(h, step, cache_id)
-        return self.ffn.forward(h, step, residuals=(x, a))
+        if self.fused_weight is None:
+            a = self.mixer.forward(h, step, cache_id)
+            return self.ffn.forward(h, step, residuals=(x, a))
+        import torch
+        from .linear import linear
+        hidden = torch.empty((h.shape[0], self.fused_weight.shape[1]), dtype=h.dtype, device=h.device)
+        self.mixer.forward_hidden(h, step, cache_id, out=hidden[:, :self.k_mixer])
+        self.ffn.forward_hidden(h, step, out=hidden[:, self.k_mixer:])
+        return linear(hidden, self.fused_weight, self.fused_bias, residuals=(x,))
 
 
 class SequentialBlock(Arrangement):

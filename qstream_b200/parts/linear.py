@@ -12,10 +12,11 @@ import torch
 from ..csrc import ops
 
 
-def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None) -> torch.Tensor:
+def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, out=None) -> torch.Tensor:
+    """`out`: an optional view [M, N] with contiguous rows (any row stride) to write into."""
     residuals = tuple(r for r in residuals if r is not None)
     if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         from ..csrc import gemm_tc
         if gemm_tc.takes(x, weight):
-            return gemm_tc.linear(x, weight, bias, activation, residuals, out_dtype)
-    return ops.linear_simt(x, weight, bias, activation, residuals, out_dtype)
+            return gemm_tc.linear(x, weight, bias, activation, residuals, out_dtype, out)
+    return ops.linear_simt(x, weight, bias, activation, residuals, out_dtype, out)

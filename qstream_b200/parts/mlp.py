@@ -29,8 +29,16 @@ class Mlp(FeedForward):
         self.down_bias = tensors.get("down_bias") if spec.bias else None
 
     def forward(self, h, step, residuals=()):
-        g = linear(h, self.up, self.up_bias, activation=self.spec.activation)
+        g = self.forward_hidden(h, step)
         return linear(g, self.down, self.down_bias, residuals=residuals)
+
+    # See Attention.output_projection: the same pair for a parallel block that fuses both projections.
+    def output_projection(self):
+        return self.down, self.down_bias
+
+    def forward_hidden(self, h, step, out=None):
+        """The activated up projection: [T, inner], written to `out` if given."""
+        return linear(h, self.up, self.up_bias, activation=self.spec.activation, out=out)
 
 
 register("feed_forward", "mlp", Mlp)
