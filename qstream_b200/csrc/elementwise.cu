@@ -97,20 +97,6 @@ __global__ void layernorm_kernel(T* __restrict__ out, const T* __restrict__ x,
     }
 }
 
-// Eight consecutive elements of a weight or bias vector stored as float32 or bfloat16 (c a multiple of 8).
-__device__ __forceinline__ void load8_as_f32(const void* p, int dtype, int c, float (&f)[8]) {
-    if (dtype == QS_F32) {
-        const float4 a = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + c)[0];
-        const float4 b = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + c)[1];
-        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-    } else {
-        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + c);
-        const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { f[2 * j] = __uint_as_float(u[j] << 16); f[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
-    }
-}
-
 // The same for bfloat16 rows whose width is a multiple of 8: one warp per row, the row kept in
 // registers as NV 16-byte pieces per lane (width <= 256 * NV), statistics by warp butterflies.
 template <int NV>

@@ -150,6 +150,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         const bool vec_ok = ep.c_dtype == QS_BF16 && (ep.ldc % 8) == 0 && ((uintptr_t)ep.C % 16) == 0 &&
                             (!ep.res1 || ((ep.ldr % 8) == 0 && ((uintptr_t)ep.res1 % 16) == 0)) &&
                             (!ep.res2 || ((uintptr_t)ep.res2 % 16) == 0);
+        const bool bias_vec = ep.bias && ((uintptr_t)ep.bias % 32) == 0;
         int i = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++i) {
             const int buf = i & 1;
@@ -169,11 +170,18 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(ep.C) + (size_t)m * ep.ldc + nc;
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        float v[8];
+                        float v[8], bv[8];
+                        if (ep.bias) {
+                            if (bias_vec) load8_as_f32(ep.bias, ep.bias_dtype, nc + g * 8, bv);
+                            else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) bv[j] = load_as_f32(ep.bias, ep.bias_dtype, nc + g * 8 + j);
+                            }
+                        }
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             float x = __uint_as_float(raw[g * 8 + j]);
-                            if (ep.bias) x += load_as_f32(ep.bias, ep.bias_dtype, nc + g * 8 + j);
+                            if (ep.bias) x += bv[j];
                             v[j] = apply_activation_fast(x, ep.act);
                         }
                         if (ep.res1) {
