@@ -39,11 +39,19 @@ constexpr float RESCALE_THRESHOLD = 8.0f;        // log2 units
 
 struct TileInfo { int row_start, n_rows, qpos0, slot; };
 
+// 2^x on the special-function unit (relative error about 2^-22; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int NKC> constexpr int kv_stages() { return NKC == 4 ? 2 : (NKC == 3 ? 3 : 4); }
 template <int NKC> constexpr int q_bytes() { return BM * KC * 2 * NKC; }
 template <int NKC> constexpr int kv_tile_bytes() { return BN * KC * 2 * NKC; }      // one of K or V
+constexpr int P_BYTES = BM * BN * 2;            // one buffer of softmax weights; there are two
 template <int NKC> constexpr int smem_bytes() {
-    return q_bytes<NKC>() + 2 * kv_stages<NKC>() * kv_tile_bytes<NKC>() + BM * BN * 2 + 1024 + 512;
+    return q_bytes<NKC>() + 2 * kv_stages<NKC>() * kv_tile_bytes<NKC>() + 2 * P_BYTES + 1024 + 512;
 }
 
 template <int NKC>
@@ -63,14 +71,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint8_t* q_smem = smem;
     uint8_t* kv_smem = q_smem + q_bytes<NKC>();          // per stage: K tile then V tile
     uint8_t* p_smem = kv_smem + 2 * STAGES * KV_TILE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + BM * BN * 2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + 2 * P_BYTES);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;
     uint64_t* v_full = k_full + STAGES;
     uint64_t* kv_empty = v_full + STAGES;
     uint64_t* s_full = kv_empty + STAGES;                // [2]
-    uint64_t* p_full = s_full + 2;
-    uint64_t* pv_done = p_full + 1;
+    uint64_t* p_full = s_full + 2;                        // [2]
+    uint64_t* p_free = p_full + 2;                        // [2]
+    uint64_t* pv_done = p_free + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
     volatile uint32_t* aborted = tmem_slot + 1;
 
@@ -88,7 +97,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
         mbar_init(&s_full[0], 1);
         mbar_init(&s_full[1], 1);
-        mbar_init(p_full, BM);
+        mbar_init(&p_full[0], BM);
+        mbar_init(&p_full[1], BM);
+        mbar_init(&p_free[0], 1);
+        mbar_init(&p_free[1], 1);
         mbar_init(pv_done, 1);
         *aborted = 0;
         mbar_fence_init();
@@ -155,10 +167,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (j + 1 < n_blocks) ok = issue_qk(j + 1);
                 if (!ok) break;
                 const int st = j % STAGES;
-                if (!mbar_wait(p_full, j & 1)) { atomicExch(status, 114); *aborted = 1; break; }
+                if (!mbar_wait(&p_full[j & 1], (j >> 1) & 1)) { atomicExch(status, 114); *aborted = 1; break; }
                 if (!mbar_wait(&v_full[st], (j / STAGES) & 1)) { atomicExch(status, 115); *aborted = 1; break; }
                 tc_fence_after_sync();
-                const uint32_t pa = smem_u32(p_smem);
+                const uint32_t pa = smem_u32(p_smem + (j & 1) * P_BYTES);
                 const uint32_t va = smem_u32(kv_smem + (size_t)st * 2 * KV_TILE + KV_TILE);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
@@ -168,10 +180,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                              smem_desc_sw128_mn(va + k * 2048, BN * KC * 2, 1024), idesc_pv, (j | k) != 0);
                 }
                 mma_commit(&kv_empty[st]);
+                mma_commit(&p_free[j & 1]);
                 mma_commit(pv_done);
             }
             if (!ok || *aborted) {                   // let the softmax warps fall through their waits
                 mma_commit(&s_full[0]); mma_commit(&s_full[1]); mma_commit(pv_done);
+                mma_commit(&p_free[0]); mma_commit(&p_free[1]);
             }
         }
     } else {
@@ -203,13 +217,16 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 s[c] = v;
                 bmax = fmaxf(bmax, v);
             }
-            // O and the P buffer are free once the previous block's P V has completed
-            if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(status, 117); ok = false; break; }
+            // Two buffers of weights: this block's buffer is free once the P V of block j - 2 has completed
+            // (a barrier per buffer), so these exponentials run under the P V of block j - 1.
+            if (j > 1 && !mbar_wait(&p_free[j & 1], ((j >> 1) - 1) & 1)) { atomicExch(status, 117); ok = false; break; }
             const bool grow = bmax > m + RESCALE_THRESHOLD || (m == -INFINITY && bmax > -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {         // tcgen05.ld/st are warp-wide: the whole warp goes
                 const float m_new = grow ? bmax : m;
-                const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);     // 1 where the row keeps its scale
+                const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);     // 1 where the row keeps its scale
                 if (j > 0) {
+                    // O may only be touched between two P V products
+                    if (!mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(status, 119); ok = false; break; }
                     tc_fence_after_sync();
                     for (int c = 0; c < NKC * 2; ++c) {
                         if (c * 32 >= dh) break;
@@ -226,15 +243,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 m = m_new;
             }
             // P = exp2(s - m), rounded to bfloat16, in the swizzled K-major layout; the sum uses the rounded values
-            uint8_t* prow = p_smem + (size_t)r * 128;
+            uint8_t* prow = p_smem + (j & 1) * P_BYTES + (size_t)r * 128;
             float psum = 0.f;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float a = m == -INFINITY ? 0.f : exp2f(s[ch * 8 + 2 * i] - m);
-                    const float b = m == -INFINITY ? 0.f : exp2f(s[ch * 8 + 2 * i + 1] - m);
+                    const float a = m == -INFINITY ? 0.f : fast_exp2(s[ch * 8 + 2 * i] - m);
+                    const float b = m == -INFINITY ? 0.f : fast_exp2(s[ch * 8 + 2 * i + 1] - m);
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(a, b);
                     psum += __bfloat162float(pb.x) + __bfloat162float(pb.y);
                     w[i] = *reinterpret_cast<const uint32_t*>(&pb);
@@ -244,7 +261,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             l += psum;
             fence_proxy_async_smem();
             tc_fence_before_sync();
-            mbar_arrive(p_full);
+            mbar_arrive(&p_full[j & 1]);
         }
         if (ok && !mbar_wait(pv_done, (n_blocks - 1) & 1)) { atomicExch(status, 118); ok = false; }
         if (ok && !*aborted) {
