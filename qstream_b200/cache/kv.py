@@ -70,23 +70,26 @@ class KvGroup:
         self.table_dev = torch.full((n_slots, max_pages), -1, dtype=torch.int32, device=device)
         self._dirty: set[int] = set()
         self.first_page = [0] * n_slots     # pages below this index were given back (window)
+        self.held = [0] * n_slots           # pages held from first_page on (they are contiguous)
 
     @property
     def bytes(self) -> int:
         return 2 * self.k.numel() * self.k.element_size()
 
     def pages_needed(self, slot: int, new_length: int) -> int:
-        have = int((self.table_host[slot] >= 0).sum()) + self.first_page[slot]
-        return max(0, -(-new_length // self.page_tokens) - have)
+        return max(0, -(-new_length // self.page_tokens) - self.first_page[slot] - self.held[slot])
 
     def ensure(self, slot: int, new_length: int) -> None:
         """Pages for positions [0, new_length) of the slot (those not given back)."""
         n = -(-new_length // self.page_tokens)
+        have = self.first_page[slot] + self.held[slot]
+        if n <= have:
+            return
         row = self.table_host[slot]
-        for i in range(self.first_page[slot], n):
-            if row[i] < 0:
-                row[i] = self.pool.alloc()
-                self._dirty.add(slot)
+        for i in range(have, n):
+            row[i] = self.pool.alloc()
+        self.held[slot] += n - have
+        self._dirty.add(slot)
 
     def trim(self, slot: int, length: int) -> None:
         """Give back pages that no later query can reach: with a window w the next
@@ -95,13 +98,16 @@ class KvGroup:
         if w <= 0:
             return
         keep_from = max(0, length - w + 1) // self.page_tokens
+        if keep_from <= self.first_page[slot]:
+            return
         row = self.table_host[slot]
         for i in range(self.first_page[slot], keep_from):
             if row[i] >= 0:
                 self.pool.free(int(row[i]))
                 row[i] = -1
+                self.held[slot] -= 1
                 self._dirty.add(slot)
-        self.first_page[slot] = max(self.first_page[slot], keep_from)
+        self.first_page[slot] = keep_from
 
     def release(self, slot: int) -> None:
         row = self.table_host[slot]
@@ -109,6 +115,7 @@ class KvGroup:
             self.pool.free(int(row[i]))
         row[:] = -1
         self.first_page[slot] = 0
+        self.held[slot] = 0
         self._dirty.add(slot)
 
     def upload(self) -> None:
@@ -200,14 +207,17 @@ class SequenceCache:
         if len(set(slots)) != len(slots):
             raise QStreamError(QsError.INVALID_INPUT, "a sequence appears twice in one step")
         need = [0] * len(self.groups)
+        lengths = self.slots.length
         for slot, n in zip(slots, n_new):
             self.slots.require(slot)
-            new_len = self.slots.length[slot] + n
+            new_len = lengths[slot] + n
             if new_len > self.max_context:
                 raise QStreamError(QsError.SEQ_TOO_LONG,
                                    f"sequence in slot {slot} would hold {new_len} tokens; the context is {self.max_context}")
             for gi, g in enumerate(self.groups):
                 need[gi] += g.pages_needed(slot, new_len)
+        if not any(need):
+            return                                      # every token of the step lands in a page already held
         for gi, g in enumerate(self.groups):
             if need[gi] > g.pool.n_free:
                 raise QStreamError(
@@ -222,9 +232,10 @@ class SequenceCache:
 
     def commit(self, slots: Sequence[int], n_new: Sequence[int]) -> None:
         """The step has been launched: lengths grow, windows let go of old pages."""
+        windowed = [g for g in self.groups if g.need.window > 0]
         for slot, n in zip(slots, n_new):
             self.slots.length[slot] += n
-            for g in self.groups:
+            for g in windowed:
                 g.trim(slot, self.slots.length[slot])
 
     def view(self, cache_id: int) -> CacheView:
