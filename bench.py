@@ -154,13 +154,24 @@ def main(argv=None) -> int:
         logits = []
         for a in range(0, batch, chunk):
             logits.append(engine.step(slots[a:a + chunk], prompts[a:a + chunk]))
-        tokens = ops.argmax(torch.cat(logits)).tolist()
+        tokens = ops.argmax(torch.cat(logits))       # stays on the device
+        host = [torch.empty(batch, dtype=torch.int32).pin_memory() for _ in range(2)]
+        copied = [None, None]
+        turn = 0
 
         def one_step():
-            nonlocal tokens
-            out = engine.step(slots, [[t] for t in tokens])
-            nxt = ops.argmax(out)
-            tokens = nxt.tolist()                   # the host reads the tokens every step, as generation does
+            # As the generation loop does it: the sampled tokens feed the next step on the device, and the
+            # host reads every step's tokens (a copy into pinned memory) while the following step runs.
+            nonlocal tokens, turn
+            out = engine.step(slots, tokens)
+            tokens = ops.argmax(out)
+            host[turn].copy_(tokens, non_blocking=True)
+            copied[turn] = torch.cuda.Event()
+            copied[turn].record()
+            turn ^= 1
+            if copied[turn] is not None:
+                copied[turn].synchronize()
+                host[turn].tolist()
 
         for _ in range(warmup):
             one_step()
@@ -241,19 +252,22 @@ def main(argv=None) -> int:
 
         # end to end: the Python entry point, host token lists in and out, every step copies the
         # step's metadata from pinned host memory and reads the chosen tokens back
-        steps = args.steps
+        steps = 2 * args.steps                          # twice the steps: the prefill before them leaves the GPU power-capped for a while
         engine = qs.Engine(model, max_tokens=args.batch * ctx, max_batch=args.batch, max_context=ctx)
         prompt_len = ctx - steps - 4
         prompts = [[int(t) for t in rng.integers(0, V, prompt_len)] for _ in range(args.batch)]
         qs.generate(engine, [p[:64] for p in prompts], max_new_tokens=4, sampling=qs.SamplingConfig.greedy(),
                     stop_tokens=())
+        t0 = sampler.mark()
         res = qs.generate(engine, prompts, max_new_tokens=steps + 1, sampling=qs.SamplingConfig.greedy(),
                           stop_tokens=())
+        t1 = sampler.mark()
         assert all(len(t) == steps + 1 for t in res.tokens)
         rows = args.batch
         line["e2e"] = {"value": round(res.decode_tokens / res.decode_seconds, 2), "unit": "tokens/s",
                        "h2d_bytes_per_step": (7 * rows + 1) * 4, "d2h_bytes_per_step": rows * 4,
-                       "prefill_tok_s": round(res.prefill_tokens / res.prefill_seconds, 1)}
+                       "prefill_tok_s": round(res.prefill_tokens / res.prefill_seconds, 1),
+                       "clocks": sampler.summary(t0, t1)}
     sampler.stop()
     print(json.dumps(line))
     return 0

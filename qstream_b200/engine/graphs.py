@@ -82,7 +82,8 @@ class DecodeGraph:
         self.launches = ops.launch_count() - before
 
     def run(self, slots, tokens, p0) -> torch.Tensor:
-        """Refresh the metadata and replay; returns the logits buffer [rows, vocab]."""
+        """Refresh the metadata and replay; returns the logits buffer [rows, vocab].
+        `tokens`: a list of ints, or an int32 device tensor [len(slots)] (no host round trip)."""
         if self.graph is None:
             self.capture()          # while the metadata still holds padding only: the warm-up run touches no sequence
         i = self.turn
@@ -90,7 +91,8 @@ class DecodeGraph:
         if self.events[i] is not None:
             self.events[i].synchronize()                # the copy that last read this buffer is done
         s, o, n = self.staging_np[i], self.offs, len(slots)
-        s[o[0]:o[0] + n] = tokens
+        on_device = isinstance(tokens, torch.Tensor)
+        s[o[0]:o[0] + n] = 0 if on_device else tokens
         s[o[0] + n:o[1]] = 0
         s[o[1]:o[1] + n] = slots
         s[o[1] + n:o[2]] = -1
@@ -101,6 +103,8 @@ class DecodeGraph:
         s[o[6]:o[6] + n] = p0
         s[o[6] + n:o[7]] = 0
         self.meta.copy_(self.staging[i], non_blocking=True)
+        if on_device:                                   # the sampler's output goes straight into the graph's input
+            self.meta[o[0]:o[0] + n].copy_(tokens, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev

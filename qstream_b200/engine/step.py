@@ -181,11 +181,18 @@ class Engine:
             return t.pin_memory().to(self.device, non_blocking=True)
         return t
 
+    accepts_device_tokens = True        # step() also takes an int32 device tensor with one token per sequence
+
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
              want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
         """Run one step.  `want[i]` lists the places among sequence i's new tokens whose
         logits are asked for (default: the last).  Returns float32 logits [n_want, vocab]
         on the device, in the order of the sequences and of `want`; None if none is wanted."""
+        if isinstance(tokens, torch.Tensor):
+            if not self.use_graphs:
+                tokens = [[int(t)] for t in tokens.tolist()]
+            else:
+                return self._decode_step(slots, tokens, want)
         if self.use_graphs and tokens and all(len(t) == 1 for t in tokens):
             return self._decode_step(slots, tokens, want)
         batch = self.build_batch(slots, tokens, want)
@@ -200,13 +207,18 @@ class Engine:
         from ..csrc import ops
         from .graphs import DecodeGraph, bucket_for
         n = len(slots)
-        if len(tokens) != n or (want is not None and len(want) != n):
+        if (not isinstance(tokens, torch.Tensor) and len(tokens) != n) or (want is not None and len(want) != n):
             raise QStreamError(QsError.INVALID_INPUT, "step: slots, tokens and want differ in length")
         V = self.model.vocab_size
-        toks = [int(t[0]) for t in tokens]
-        for s, tok in zip(slots, toks):
-            if not 0 <= tok < V:
-                raise QStreamError(QsError.INVALID_INPUT, f"token id {tok} (slot {s}) outside the vocabulary of {V}")
+        if isinstance(tokens, torch.Tensor):            # one token per sequence, already on the device (from the sampler)
+            if tokens.dtype != torch.int32 or tokens.numel() != n or not tokens.is_cuda or not tokens.is_contiguous():
+                raise QStreamError(QsError.INVALID_INPUT, "step: device tokens must be a contiguous int32 tensor, one per sequence")
+            toks = tokens
+        else:
+            toks = [int(t[0]) for t in tokens]
+            for s, tok in zip(slots, toks):
+                if not 0 <= tok < V:
+                    raise QStreamError(QsError.INVALID_INPUT, f"token id {tok} (slot {s}) outside the vocabulary of {V}")
         if want is not None:
             for w in want:
                 if any(p != 0 for p in w):
