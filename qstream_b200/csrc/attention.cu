@@ -75,6 +75,64 @@ __global__ void rope_store_kernel(T* __restrict__ q, const T* __restrict__ k, co
     }
 }
 
+// The same for bfloat16 with 16-byte accesses: an item is eight consecutive dims (four rotary pairs).
+// Needs head size and rotary width multiples of 8 and 16-byte aligned rows.
+__device__ __forceinline__ uint4 rotate8(const uint4 raw, const float* __restrict__ cs8) {
+    // cs8: (cos, sin) of the four pairs, eight floats
+    const float4 a = reinterpret_cast<const float4*>(cs8)[0], b = reinterpret_cast<const float4*>(cs8)[1];
+    const float c[4] = {a.x, a.z, b.x, b.z}, sn[4] = {a.y, a.w, b.y, b.w};
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float x = __uint_as_float(w[i] << 16), y = __uint_as_float(w[i] & 0xffff0000u);
+        const __nv_bfloat162 r = __floats2bfloat162_rn(x * c[i] - y * sn[i], x * sn[i] + y * c[i]);
+        o[i] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                                      const __nv_bfloat16* __restrict__ v, size_t ldq, size_t ldk, size_t ldv,
+                                      int n_heads, int n_kv_heads, int dh, int R,
+                                      const float* __restrict__ cos_sin, int max_pos,
+                                      const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
+                                      const int32_t* __restrict__ page_table, int max_pages, int page_shift,
+                                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                      int32_t* __restrict__ status) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int t = blockIdx.x;
+    const int tid = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
+    const int slot = tok_slot[t];
+    if (slot < 0) return;
+    const int pos = tok_pos[t];
+    const int page_tokens = 1 << page_shift;
+    const bool rotate = cos_sin != nullptr && R > 0;
+    if (rotate && (pos < 0 || pos >= max_pos)) { if (threadIdx.x == 0) atomicExch(status, 1); return; }
+    const float* cs = rotate ? cos_sin + (size_t)pos * R : nullptr;
+    const int rc = R >> 3, hc = dh >> 3;                                 // 16-byte chunks of the rotary part / of a head
+    if (q && rotate) {
+        for (int e = tid; e < n_heads * rc; e += stride) {
+            const int head = e / rc, c = e - head * rc;
+            uint4* p = reinterpret_cast<uint4*>(q + (size_t)t * ldq + (size_t)head * dh + c * 8);
+            *p = rotate8(*p, cs + c * 8);
+        }
+    }
+    if (n_kv_heads == 0) return;
+    const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
+    if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
+    const size_t in_page = (size_t)(pos & (page_tokens - 1)) * dh;
+    for (int e = tid; e < n_kv_heads * hc; e += stride) {
+        const int kvh = e / hc, c = e - kvh * hc;
+        const size_t dst = ((size_t)page * n_kv_heads + kvh) * page_tokens * dh + in_page + c * 8;
+        uint4 kk = *reinterpret_cast<const uint4*>(k + (size_t)t * ldk + (size_t)kvh * dh + c * 8);
+        if (rotate && c < rc) kk = rotate8(kk, cs + c * 8);
+        *reinterpret_cast<uint4*>(k_cache + dst) = kk;
+        *reinterpret_cast<uint4*>(v_cache + dst) = *reinterpret_cast<const uint4*>(v + (size_t)t * ldv + (size_t)kvh * dh + c * 8);
+    }
+}
+
 // ----------------------------------------------------------------------------- attention
 
 // One warp per (token, query head).  Keys are visited 32 at a time in position order:
@@ -212,6 +270,21 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
     int per_token = 1;                       // few tokens (decode): several blocks per token
     if (T_tokens < 256) { per_token = (n_kv_heads * dh / 2 + threads - 1) / threads; if (per_token > 16) per_token = 16; if (per_token < 1) per_token = 1; }
     dim3 grid(T_tokens, per_token);
+    const bool aligned = dh % 8 == 0 && R % 8 == 0 && ldq % 8 == 0 && ldk % 8 == 0 && ldv % 8 == 0 &&
+                         ((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0 &&
+                         ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 && ((uintptr_t)cos_sin % 16) == 0;
+    if (dtype == QS_BF16 && aligned) {
+        const int work8 = (n_heads * (R / 8) + n_kv_heads * (dh / 8));
+        const int threads8 = work8 >= 512 ? 128 : 64;
+        int per = 1;
+        if (T_tokens < 256) { per = (n_kv_heads * (dh / 8) + threads8 - 1) / threads8; if (per > 16) per = 16; if (per < 1) per = 1; }
+        cudaError_t e = qs_launch_dependent(rope_store_vec_kernel, dim3(T_tokens, per), dim3(threads8), 0, stream,
+            (__nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (size_t)ldq, (size_t)ldk, (size_t)ldv,
+            n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos, page_table, max_pages, shift,
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status);
+        if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "rope_store: %s", cudaGetErrorString(e));
+        return qs_check_launch("rope_store");
+    }
     if (dtype == QS_F32)
         qs_launch_dependent(rope_store_kernel<float>, grid, dim3(threads), 0, stream, (float*)q, (const float*)k, (const float*)v,
             (size_t)ldq, (size_t)ldk, (size_t)ldv, n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos,
