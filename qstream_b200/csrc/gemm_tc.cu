@@ -219,6 +219,179 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ----------------------------------------------------------------------------- persistent kernel on CTA pairs
+
+constexpr int PAIR_STAGE = BM * BK * 2 * 2;           // per CTA and stage: 128 rows of A and 128 rows of W, 64 wide
+constexpr int PAIR_STAGES = SMEM_BUDGET_BIG / PAIR_STAGE;
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE + 1024 + 512;
+constexpr int PAIR_BN = 256;
+
+// Like wait_or_abort, and it also gives up when any CTA of the grid has reported a failure.
+__device__ __forceinline__ bool wait_or_abort_grid(uint64_t* bar, uint32_t parity, volatile uint32_t* aborted,
+                                                   const int32_t* status) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && (*aborted || *reinterpret_cast<const volatile int32_t*>(status) != 0)) return false;
+    }
+    return false;
+}
+
+// Two CTAs on neighbouring SMs work on one 256 x 256 output tile with tcgen05.mma.cta_group::2: each CTA
+// loads its own 128 rows of A and its own half (128 rows) of the W tile - half the shared-memory traffic
+// per flop of the single-CTA kernel - and holds its 128 x 256 half of the accumulator in its TMEM.  The
+// even CTA (the leader) issues the MMAs for both; all TMA bytes of a stage are counted on the leader's
+// barrier; tcgen05.commit tells both CTAs when a stage or an accumulator may be used again; the other
+// CTA's epilogue warps signal the leader across the cluster.  No load uses multicast.
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const Epilogue ep, const int K, const int m_pairs, const int n_tiles,
+                    int32_t* __restrict__ status) {
+    constexpr uint32_t TMEM_COLS = 2 * PAIR_BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE);
+    uint64_t* empty = full + PAIR_STAGES;
+    uint64_t* acc_full = empty + PAIR_STAGES;         // [2]
+    uint64_t* acc_empty = acc_full + 2;               // [2], the leader's counts both CTAs' epilogue threads
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile uint32_t* aborted = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader
+    const int pair = blockIdx.x >> 1, n_pairs_grid = gridDim.x >> 1;
+    const int num_kb = (K + BK - 1) / BK;
+    const int total_tiles = m_pairs * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
+        *aborted = 0;
+        mbar_fence_init();
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_w);
+    }
+    if (warp == 1) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();                                   // both CTAs' barriers exist before anyone signals across
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t it = 0;
+            for (int t = pair; t < total_tiles && !*aborted; t += n_pairs_grid) {
+                const int m0 = (t % m_pairs) * 2 * BM + (int)rank * BM;
+                const int n0 = (t / m_pairs) * PAIR_BN + (int)rank * (PAIR_BN / 2);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    if (!wait_or_abort_grid(&empty[s], ((it / PAIR_STAGES) & 1) ^ 1, aborted, status)) { atomicExch(status, 151); *aborted = 1; break; }
+                    uint8_t* st = smem + s * PAIR_STAGE;
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * PAIR_STAGE);     // both CTAs' bytes
+                    tma_load_2d_pair(st, &map_a, &full[s], kb * BK, m0);
+                    tma_load_2d_pair(st + BM * BK * 2, &map_w, &full[s], kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, PAIR_BN);
+            uint32_t it = 0;
+            int i = 0;
+            for (int t = pair; t < total_tiles && !*aborted; t += n_pairs_grid, ++i) {
+                const int buf = i & 1;
+                if (!wait_or_abort_grid(&acc_empty[buf], ((i >> 1) & 1) ^ 1, aborted, status)) { atomicExch(status, 152); *aborted = 1; break; }
+                tc_fence_after_sync();
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % PAIR_STAGES;
+                    if (!wait_or_abort_grid(&full[s], (it / PAIR_STAGES) & 1, aborted, status)) { atomicExch(status, 153); *aborted = 1; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(smem + s * PAIR_STAGE);
+                    const uint64_t da = smem_desc_sw128(a_addr);
+                    const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        mma_bf16_pair(tmem_base + (uint32_t)(buf * PAIR_BN), da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    mma_commit_pair(&empty[s], 3);
+                }
+                mma_commit_pair(&acc_full[buf], 3);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        const bool vec_ok = ep.c_dtype == QS_BF16 && (ep.ldc % 8) == 0 && ((uintptr_t)ep.C % 16) == 0 &&
+                            (!ep.res1 || ((ep.ldr % 8) == 0 && ((uintptr_t)ep.res1 % 16) == 0)) &&
+                            (!ep.res2 || ((uintptr_t)ep.res2 % 16) == 0);
+        const bool bias_vec = ep.bias && ((uintptr_t)ep.bias % 32) == 0;
+        const uint32_t leader_acc_empty[2] = {map_to_cta(&acc_empty[0], 0), map_to_cta(&acc_empty[1], 0)};
+        int i = 0;
+        for (int t = pair; t < total_tiles; t += n_pairs_grid, ++i) {
+            const int buf = i & 1;
+            const int m = (t % m_pairs) * 2 * BM + (int)rank * BM + r, n0 = (t / m_pairs) * PAIR_BN;
+            if (!wait_or_abort_grid(&acc_full[buf], (i >> 1) & 1, aborted, status)) { atomicExch(status, 154); *aborted = 1; break; }
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < PAIR_BN / 32; ++c) {
+                uint32_t raw[32];
+                tmem_load_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * PAIR_BN + c * 32), raw);
+                tmem_load_wait();
+                const int nc = n0 + c * 32;
+                if (m >= ep.M || nc >= ep.N) continue;
+                if (vec_ok && nc + 32 <= ep.N) {
+                    __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(ep.C) + (size_t)m * ep.ldc + nc;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        float v[8], bv[8];
+                        if (ep.bias) {
+                            if (bias_vec) load8_as_f32(ep.bias, ep.bias_dtype, nc + g * 8, bv);
+                            else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) bv[j] = load_as_f32(ep.bias, ep.bias_dtype, nc + g * 8 + j);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float x = __uint_as_float(raw[g * 8 + j]);
+                            if (ep.bias) x += bv[j];
+                            v[j] = apply_activation_fast(x, ep.act);
+                        }
+                        if (ep.res1) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + nc + g * 8);
+                            const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u); }
+                        }
+                        if (ep.res2) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res2 + (size_t)m * ep.ldr + nc + g * 8);
+                            const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u); }
+                        }
+                        uint32_t o[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const __nv_bfloat162 pb = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            o[j] = *reinterpret_cast<const uint32_t*>(&pb);
+                        }
+                        *reinterpret_cast<uint4*>(crow + g * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (nc + j < ep.N) store_out(ep, m, nc + j, __uint_as_float(raw[j]));
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive_cluster(leader_acc_empty[buf]);   // the leader's MMA warp waits for both CTAs' epilogues
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();                                   // nobody leaves while the other may still signal it
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
 // ----------------------------------------------------------------------------- stream-K kernel (few tokens)
 
 template <int BN> constexpr int s_stages() { return SMEM_BUDGET_BIG / stage_bytes<BN>(); }
@@ -510,6 +683,42 @@ int launch_stream(const CUtensorMap& mw, const CUtensorMap& ma, const Epilogue& 
     return qs_check_launch("gemm_tc stream");
 }
 
+// The CTA-pair kernel as a cluster launch; `*launched` tells whether this device can run it at all.
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const Epilogue& ep, int M, int N, int K,
+                int32_t* status, cudaStream_t stream, bool* launched) {
+    static int state = 0;                 // 0 = not probed, 1 = usable, -1 = not usable
+    static int max_clusters = 0;
+    *launched = false;
+    if (state == 0) {
+        state = -1;
+        if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = PAIR_SMEM;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr; cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel, &cfg) == cudaSuccess && n > 0) { max_clusters = n; state = 1; }
+        }
+        cudaGetLastError();
+    }
+    if (state != 1) return QS_OK;
+    const int m_pairs = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + PAIR_BN - 1) / PAIR_BN;
+    const long long total = (long long)m_pairs * n_tiles;
+    const int clusters = (int)(total < max_clusters ? total : max_clusters);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = PAIR_SMEM; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, ma, mw, ep, K, m_pairs, n_tiles, status);
+    if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc pair: %s", cudaGetErrorString(e));
+    *launched = true;
+    return qs_check_launch("gemm_tc pair");
+}
+
 template <int BN>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const Epilogue& ep, int M, int N, int K,
                       int32_t* status, cudaStream_t stream) {
@@ -555,6 +764,12 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
     if (M > 64) {
         QS_REQUIRE((M + BM - 1) / BM <= 65535 * 1 && (N + 127) / 128 <= 65535, "gemm_tc: sizes exceed the grid");
         if ((rc = tensor_map(&ma, A, M, K, lda, BM)) != QS_OK) return rc;
+        if (M > BM && N > 128) {                     // enough rows for a pair of CTAs: 256 x 256 tiles
+            if ((rc = tensor_map(&mw, W, N, K, K, BM)) != QS_OK) return rc;
+            bool launched = false;
+            rc = launch_pair(ma, mw, ep, M, N, K, status, stream, &launched);
+            if (rc != QS_OK || launched) return rc;
+        }
         const int bn = N > 128 ? 256 : 128;
         if ((rc = tensor_map(&mw, W, N, K, K, bn)) != QS_OK) return rc;
         if (bn == 256) return launch_persistent<256>(ma, mw, ep, M, N, K, status, stream);
