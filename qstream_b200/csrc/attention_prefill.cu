@@ -4,7 +4,8 @@
 //   S = Q K^T        tcgen05.mma, Q [128 x dh] and K [64 x dh] both K-major in shared memory (TMA,
 //                    128-byte swizzle), S [128 x 64] float32 in TMEM (two buffers)
 //   softmax          four warps, one thread per query row: tcgen05.ld S, scale, causal / window mask,
-//                    running maximum and sum in 32-bit, P = exp2(s - m) rounded to bfloat16 and
+//                    running maximum and sum in 32-bit, P = exp2(s - m) rounded to bfloat16 (the sum is
+//                    taken over the unrounded weights) and
 //                    written to shared memory in the swizzled K-major layout the MMA reads
 //   O += P V         tcgen05.mma, V [64 keys x dh] as the page lies in the cache (MN-major), O
 //                    [128 x dh] float32 in TMEM; O is rescaled in TMEM only when a row's maximum has
@@ -208,15 +209,22 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tmem_load_wait();
             const int key0 = (block_first + j) * BN;
             const bool all_visible = key0 + BN - 1 <= qpos && key0 >= lo;
-            float s[BN];
-            float bmax = -INFINITY;
+            // raw scores stay in `raw`; masked ones become -inf.  The maximum is taken over four independent
+            // chains (the thread has no other warp to hide a 64-long dependent chain behind).
+            if (!all_visible) {
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                float v = __uint_as_float(raw[c >> 5][c & 31]) * scale_log2;
-                if (!all_visible) { const int key = key0 + c; if (key > qpos || key < lo) v = -INFINITY; }
-                s[c] = v;
-                bmax = fmaxf(bmax, v);
+                for (int c = 0; c < BN; ++c) {
+                    const int key = key0 + c;
+                    if (key > qpos || key < lo) raw[c >> 5][c & 31] = 0xff800000u;       // -inf
+                }
             }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < BN; c += 4) {
+#pragma unroll
+                for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(raw[(c + u) >> 5][(c + u) & 31]));
+            }
+            const float bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;    // scale_log2 > 0
             // Two buffers of weights: this block's buffer is free once the P V of block j - 2 has completed
             // (a barrier per buffer), so these exponentials run under the P V of block j - 1.
             if (j > 1 && !mbar_wait(&p_free[j & 1], ((j >> 1) - 1) & 1)) { atomicExch(status, 117); ok = false; break; }
@@ -242,23 +250,28 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 l *= alpha;
                 m = m_new;
             }
-            // P = exp2(s - m), rounded to bfloat16, in the swizzled K-major layout; the sum uses the rounded values
+            // P = exp2(s * scale - m) (one FMA and one ex2 per score), rounded to bfloat16 and written in the
+            // swizzled K-major layout; the row sum is taken in 32-bit over two independent chains.
             uint8_t* prow = p_smem + (j & 1) * P_BYTES + (size_t)r * 128;
-            float psum = 0.f;
+            const float neg_m = m == -INFINITY ? -INFINITY : -m;          // a row with no visible key so far: all weights 0
+            float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float a = m == -INFINITY ? 0.f : fast_exp2(s[ch * 8 + 2 * i] - m);
-                    const float b = m == -INFINITY ? 0.f : fast_exp2(s[ch * 8 + 2 * i + 1] - m);
+                    const int c = ch * 8 + 2 * i;
+                    const float sa = __uint_as_float(raw[c >> 5][c & 31]), sb = __uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]);
+                    const float a = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sa, scale_log2, neg_m));
+                    const float b = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sb, scale_log2, neg_m));
+                    ps0 += a;
+                    ps1 += b;
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(a, b);
-                    psum += __bfloat162float(pb.x) + __bfloat162float(pb.y);
                     w[i] = *reinterpret_cast<const uint32_t*>(&pb);
                 }
                 *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            l += psum;
+            l += ps0 + ps1;
             fence_proxy_async_smem();
             tc_fence_before_sync();
             mbar_arrive(&p_full[j & 1]);
