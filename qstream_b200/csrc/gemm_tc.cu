@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -394,8 +395,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // ----------------------------------------------------------------------------- stream-K kernel (few tokens)
 
-template <int BN> constexpr int s_stages() { return SMEM_BUDGET_BIG / stage_bytes<BN>(); }
-template <int BN> constexpr int s_smem_bytes() { return s_stages<BN>() * stage_bytes<BN>() + 1024 + 512; }
 
 // The CTA that holds work unit u when U units are dealt to G CTAs as [c U / G, (c + 1) U / G).
 __device__ __forceinline__ int owner_of(long long u, long long U, int G) { return (int)(((u + 1) * G - 1) / U); }
@@ -408,25 +407,31 @@ __device__ __forceinline__ int owner_of(long long u, long long U, int G) { retur
 // CTA, an arrival counter per tile tells the last contributor, and that CTA adds the partial tiles in
 // ascending k (ascending CTA) order and runs the epilogue.  No CTA ever waits for another.  The dealing
 // depends on N, K and the device only, so a token's result does not depend on its batch.
+constexpr int MAX_STREAM_STAGES = 40;
+constexpr int STREAM_PAD = BM * BK * 2;          // the MMA always reads 128 rows from a slot: room behind the last one
+
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
-                      const Epilogue ep, const int K, const int tiles, float* __restrict__ ws,
-                      int32_t* __restrict__ counters, int32_t* __restrict__ status) {
-    constexpr int STAGES = s_stages<BN>();
-    constexpr int STAGE = stage_bytes<BN>();
+                      const Epilogue ep, const int K, const int tiles, const int tile_rows, const int STAGES,
+                      float* __restrict__ ws, int32_t* __restrict__ counters, int32_t* __restrict__ status) {
+    // A tile is `tile_rows` (a multiple of 8, at most 128) output features high: narrow or uneven N is cut
+    // into as many equal tiles as there are SMs.  The MMA still spans 128 rows; rows past tile_rows hold
+    // whatever lies behind the slot and are never stored.
+    const int STAGE = tile_rows * BK * 2 + BN * BK * 2;
     constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     constexpr int CH = BN < 32 ? 16 : 32;
 
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE);
-    uint64_t* empty = full + STAGES;
-    uint64_t* acc_full = empty + STAGES;              // [2]
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(base);
+    uint64_t* empty = full + MAX_STREAM_STAGES;
+    uint64_t* acc_full = empty + MAX_STREAM_STAGES;   // [2]
     uint64_t* acc_empty = acc_full + 2;               // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* aborted = tmem_slot + 1;
     volatile uint32_t* last_flag = tmem_slot + 2;
+    uint8_t* smem = base + 1024;                      // the ring of stages
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (K + BK - 1) / BK;
@@ -449,74 +454,89 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const uint32_t tmem_base = *tmem_slot;
     grid_dep_launch();                                // the next kernel may be scheduled as CTAs of this one leave
 
+    // The loops of the two single threads carry their tile, k-block, stage and phase along: a division
+    // in a lone thread's dependent chain costs as much as the copy it is about to start.
+    const int tile_begin = (int)(u_begin / total_kb), kb_begin = (int)(u_begin - (long long)tile_begin * total_kb);
+    const int count = (int)(u_end - u_begin);
+
     if (warp == 0) {
         if (elect_one()) {
             // The weights are written by no kernel: the ring is filled with tiles of W right away, while the
             // previous kernel may still be running; the tokens' tiles follow once it has completed.
-            const int ahead = (int)min((long long)STAGES, u_end - u_begin);
+            const int ahead = min(STAGES, count);
+            int tile = tile_begin, kb = kb_begin;
             for (int i = 0; i < ahead; ++i) {
-                const long long u = u_begin + i;
-                const int tile = (int)(u / total_kb), kb = (int)(u - (long long)tile * total_kb);
                 mbar_expect_tx(&full[i], STAGE);
-                tma_load_2d(smem + i * STAGE, &map_w, &full[i], kb * BK, tile * BM);
+                tma_load_2d(smem + i * STAGE, &map_w, &full[i], kb * BK, tile * tile_rows);
+                if (++kb == total_kb) { kb = 0; ++tile; }
             }
             grid_dep_wait();
+            kb = kb_begin;
             for (int i = 0; i < ahead; ++i) {
-                const long long u = u_begin + i;
-                const int kb = (int)(u % total_kb);
-                tma_load_2d(smem + i * STAGE + BM * BK * 2, &map_a, &full[i], kb * BK, 0);
+                tma_load_2d(smem + i * STAGE + tile_rows * BK * 2, &map_a, &full[i], kb * BK, 0);
+                if (++kb == total_kb) kb = 0;
             }
-            uint32_t it = ahead;
-            for (long long u = u_begin + ahead; u < u_end && !*aborted; ++u, ++it) {
-                const int tile = (int)(u / total_kb), kb = (int)(u - (long long)tile * total_kb);
-                const int s = it % STAGES;
-                if (!wait_or_abort(&empty[s], ((it / STAGES) & 1) ^ 1, aborted)) { atomicExch(status, 131); *aborted = 1; break; }
+            int s = ahead == STAGES ? 0 : ahead;
+            uint32_t parity = ahead == STAGES ? 0u : 1u;      // the phase of empty[s] that frees the slot
+            for (int i = ahead; i < count; ++i) {
+                if (!wait_or_abort(&empty[s], parity, aborted)) { atomicExch(status, 131); *aborted = 1; break; }
                 uint8_t* st = smem + s * STAGE;
                 mbar_expect_tx(&full[s], STAGE);
-                tma_load_2d(st, &map_w, &full[s], kb * BK, tile * BM);
-                tma_load_2d(st + BM * BK * 2, &map_a, &full[s], kb * BK, 0);
+                tma_load_2d(st, &map_w, &full[s], kb * BK, tile * tile_rows);
+                tma_load_2d(st + tile_rows * BK * 2, &map_a, &full[s], kb * BK, 0);
+                if (++kb == total_kb) { kb = 0; ++tile; }
+                if (++s == STAGES) { s = 0; parity ^= 1u; }
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
             constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
-            uint32_t it = 0;
-            int seg = 0;
-            for (long long u = u_begin; u < u_end && !*aborted; ++seg) {
-                const int tile = (int)(u / total_kb), kb0 = (int)(u - (long long)tile * total_kb);
-                const int n = (int)min((long long)(total_kb - kb0), u_end - u);
+            int s = 0, kb0 = kb_begin, left = count, seg = 0;
+            uint32_t parity = 0;
+            for (; left > 0; ++seg) {
+                const int n = min(total_kb - kb0, left);
                 const int buf = seg & 1;
                 if (!wait_or_abort(&acc_empty[buf], ((seg >> 1) & 1) ^ 1, aborted)) { atomicExch(status, 132); *aborted = 1; break; }
                 tc_fence_after_sync();
-                for (int kb = 0; kb < n; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    if (!wait_or_abort(&full[s], (it / STAGES) & 1, aborted)) { atomicExch(status, 133); *aborted = 1; break; }
+                bool ok = true;
+                for (int kb = 0; kb < n; ++kb) {
+                    if (!wait_or_abort(&full[s], parity, aborted)) { atomicExch(status, 133); *aborted = 1; ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t w_addr = smem_u32(smem + s * STAGE);
                     const uint64_t dw = smem_desc_sw128(w_addr);
-                    const uint64_t da = smem_desc_sw128(w_addr + BM * BK * 2);
+                    const uint64_t da = smem_desc_sw128(w_addr + tile_rows * BK * 2);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
                         mma_bf16(tmem_base + (uint32_t)(buf * BN), dw + 2 * k, da + 2 * k, idesc, (kb | k) != 0);
                     mma_commit(&empty[s]);
+                    if (++s == STAGES) { s = 0; parity ^= 1u; }
                 }
                 mma_commit(&acc_full[buf]);
-                u += n;
+                if (!ok) break;
+                left -= n;
+                kb0 = 0;
             }
         }
     } else {
         const int quad = warp & 3;
         const int r = quad * 32 + lane;                   // TMEM lane = output feature within the tile
         grid_dep_wait();                                  // residuals, outputs and the workspace belong to earlier kernels until now
-        int seg = 0;
-        for (long long u = u_begin; u < u_end; ++seg) {
-            const int tile = (int)(u / total_kb), kb0 = (int)(u - (long long)tile * total_kb);
-            const int n = (int)min((long long)(total_kb - kb0), u_end - u);
+        int seg = 0, tile = tile_begin, kb0 = kb_begin, left = count;
+        for (; left > 0; ++seg, ++tile, kb0 = 0) {
+            const int n = min(total_kb - kb0, left);
+            left -= n;
             const int buf = seg & 1;
-            const int feat = tile * BM + r;
+            const int feat = r < tile_rows ? tile * tile_rows + r : ep.N;       // rows past the tile's height are not stored
             if (!wait_or_abort(&acc_full[buf], (seg >> 1) & 1, aborted)) { atomicExch(status, 134); *aborted = 1; break; }
             tc_fence_after_sync();
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+            auto load_acc = [&](int c, float (&v)[CH]) {
+                uint32_t raw[CH];
+                if constexpr (CH == 32) tmem_load_32x32(tacc + c * CH, raw); else tmem_load_32x16(tacc + c * CH, raw);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(raw[j]);
+            };
             auto emit = [&](int c, const float (&v)[CH]) {
                 if (feat < ep.N) {
 #pragma unroll
@@ -529,12 +549,8 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (n == total_kb) {                          // the whole tile was accumulated here
 #pragma unroll 1
                 for (int c = 0; c < BN / CH; ++c) {
-                    uint32_t raw[CH];
-                    if constexpr (CH == 32) tmem_load_32x32(tacc + c * CH, raw); else tmem_load_32x16(tacc + c * CH, raw);
-                    tmem_load_wait();
                     float v[CH];
-#pragma unroll
-                    for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(raw[j]);
+                    load_acc(c, v);
                     emit(c, v);
                 }
             } else {
@@ -542,11 +558,11 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 float* mine = ws + ((size_t)cta * 2 + (seg == 0 ? 0 : 1)) * BN * BM;
 #pragma unroll 1
                 for (int c = 0; c < BN / CH; ++c) {
-                    uint32_t raw[CH];
-                    if constexpr (CH == 32) tmem_load_32x32(tacc + c * CH, raw); else tmem_load_32x16(tacc + c * CH, raw);
-                    tmem_load_wait();
+                    float pv[CH];
+                    load_acc(c, pv);
 #pragma unroll
-                    for (int j = 0; j < CH; ++j) mine[(size_t)(c * CH + j) * BM + r] = __uint_as_float(raw[j]);
+                    for (int j = 0; j < CH; ++j)
+                        if (r < tile_rows) mine[(size_t)(c * CH + j) * BM + r] = pv[j];
                 }
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -566,7 +582,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                         float v[CH];
 #pragma unroll
                         for (int j = 0; j < CH; ++j) v[j] = 0.f;
-                        for (int cc = c_first; cc <= c_last; ++cc) {
+                        for (int cc = c_first; cc <= c_last && r < tile_rows; ++cc) {
                             const int first_tile = (int)(((long long)cc * U / G) / total_kb);
                             const float* part = ws + ((size_t)cc * 2 + (first_tile == tile ? 0 : 1)) * BN * BM;
 #pragma unroll
@@ -579,7 +595,6 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             }
             tc_fence_before_sync();
             mbar_arrive(&acc_empty[buf]);
-            u += n;
         }
     }
     tc_fence_before_sync();
@@ -649,13 +664,13 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
 }
 
 template <int BN>
-int launch_stream(const CUtensorMap& mw, const CUtensorMap& ma, const Epilogue& ep, int N, int K, float* ws,
+int launch_stream(const void* W, const CUtensorMap& ma, const Epilogue& ep, int N, int K, float* ws,
                   long long ws_floats, int32_t* counters, int n_counters, int32_t* status, cudaStream_t stream) {
     static bool configured = false;
     static int sm_count = 0;
+    constexpr int SMEM_MAX = 224 * 1024;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_stream_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             s_smem_bytes<BN>());
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_stream_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX);
         int dev = 0;
         if (e == cudaSuccess) e = cudaGetDevice(&dev);
         if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
@@ -663,22 +678,37 @@ int launch_stream(const CUtensorMap& mw, const CUtensorMap& ma, const Epilogue& 
                                              cudaGetErrorString(e));
         configured = true;
     }
-    const int tiles = (N + BM - 1) / BM;
+    // One CTA per SM with a ring that fills its shared memory.  N is cut into whole tiles of equal height
+    // (8..128 rows), as many as fill the SMs an integral number of times, so that every SM streams its
+    // share of W and no partial sums are needed.  Where such tiles would still leave a tenth of the SMs
+    // idle (a narrow N), tiles of full height are dealt by k-blocks instead (stream-K) and the CTAs that
+    // share a tile add their partial tiles.  The dealing depends on N, K and the device only.
     const long long total_kb = (K + BK - 1) / BK;
-    const long long U = tiles * total_kb;
-    // One CTA per SM with a ring that fills its shared memory.  With enough tiles to occupy most SMs every
-    // CTA takes whole tiles (no partial sums at all); with fewer (a narrow N) the k-blocks are dealt evenly
-    // to one CTA per SM, in shares of at least MIN_KB_PER_SPLIT.  Both depend on N, K and the device only.
-    long long G = sm_count;
-    if (tiles * 5 >= (long long)sm_count * 3) G = tiles;
-    else {
-        if (G > U / MIN_KB_PER_SPLIT) G = U / MIN_KB_PER_SPLIT;
-        if (G < 1) G = 1;
-        if (!ws || !counters || tiles > n_counters || G * 2 * BN * BM > ws_floats) G = tiles;
+    const long long waves = ((long long)N + (long long)BM * sm_count - 1) / ((long long)BM * sm_count);
+    long long rows = (N + waves * sm_count - 1) / (waves * sm_count);
+    rows = (rows + 7) / 8 * 8;
+    if (rows > BM) rows = BM;
+    long long tiles = (N + rows - 1) / rows;
+    long long G = tiles;
+    if (tiles * 10 < (tiles + sm_count - 1) / sm_count * sm_count * 9) {
+        const long long full_tiles = (N + BM - 1) / BM;
+        long long g = sm_count;
+        if (g > full_tiles * total_kb / MIN_KB_PER_SPLIT) g = full_tiles * total_kb / MIN_KB_PER_SPLIT;
+        if (ws && counters && g > full_tiles && full_tiles <= n_counters && g * 2 * BN * BM <= ws_floats) {
+            rows = BM;
+            tiles = full_tiles;
+            G = g;
+        }
     }
-    QS_REQUIRE(tiles <= n_counters || !counters, "gemm_tc: %d tiles exceed the %d arrival counters", tiles, n_counters);
-    cudaError_t e = qs_launch_dependent(gemm_tc_stream_kernel<BN>, dim3((unsigned)G), dim3(THREADS), s_smem_bytes<BN>(), stream,
-                                        mw, ma, ep, K, tiles, ws, counters, status);
+    const int stage = (int)rows * BK * 2 + BN * BK * 2;
+    int stages = (SMEM_MAX - 2048 - STREAM_PAD) / stage;
+    if (stages > MAX_STREAM_STAGES) stages = MAX_STREAM_STAGES;
+    const int smem = 2048 + stages * stage + STREAM_PAD;
+    CUtensorMap mw;
+    int rc = tensor_map(&mw, W, N, K, K, (int)rows);
+    if (rc != QS_OK) return rc;
+    cudaError_t e = qs_launch_dependent(gemm_tc_stream_kernel<BN>, dim3((unsigned)G), dim3(THREADS), (size_t)smem, stream,
+                                        mw, ma, ep, K, (int)tiles, (int)rows, stages, ws, counters, status);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc stream: %s", cudaGetErrorString(e));
     return qs_check_launch("gemm_tc stream");
 }
@@ -776,9 +806,8 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
         return launch_persistent<128>(ma, mw, ep, M, N, K, status, stream);
     }
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    if ((rc = tensor_map(&mw, W, N, K, K, BM)) != QS_OK) return rc;
     if ((rc = tensor_map(&ma, A, M, K, lda, bn)) != QS_OK) return rc;
-    if (bn == 16) return launch_stream<16>(mw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    if (bn == 32) return launch_stream<32>(mw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    return launch_stream<64>(mw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    if (bn == 16) return launch_stream<16>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    if (bn == 32) return launch_stream<32>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    return launch_stream<64>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
 }
