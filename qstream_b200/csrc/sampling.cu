@@ -33,36 +33,58 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
-// Greedy: strict '>' scan, so the lowest index wins ties (src/sampling.c:214-224).
-__global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict__ logits,
-                              int V, size_t ld) {
-    __shared__ float best_v[32];
-    __shared__ int best_i[32];
+// Greedy: strict '>' scan from element 0, so the lowest index wins ties, a NaN is never chosen over a
+// number, and a row that begins with NaN yields 0 (src/sampling.c:214-224).  Value and index are packed
+// into one 64-bit key whose maximum is that element: the value's order key above, the complement of
+// the index below.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
+    if (v != v) return i == 0 ? ~0ull : 0ull;
+    if (v == 0.0f) v = 0.0f;                          // -0 and +0 compare equal
+    return ((unsigned long long)order_key(v) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)i);
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(int32_t* __restrict__ out, const float* __restrict__ logits, int V, size_t ld) {
+    __shared__ unsigned long long best[32];
     const float* row = logits + (size_t)blockIdx.x * ld;
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) { bv = v; bi = i; }
+    unsigned long long key = 0;
+    // scalar head up to a 16-byte boundary, 16-byte body, scalar tail
+    const int head = min(V, (int)((4 - ((reinterpret_cast<uintptr_t>(row) >> 2) & 3)) & 3));
+    const int n4 = (V - head) >> 2;
+    if ((int)threadIdx.x < head) key = argmax_key(row[threadIdx.x], threadIdx.x);
+    const float4* body = reinterpret_cast<const float4*>(row + head);
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+        const float4 v = body[j];
+        const int i = head + 4 * j;
+        unsigned long long k0 = argmax_key(v.x, i), k1 = argmax_key(v.y, i + 1);
+        unsigned long long k2 = argmax_key(v.z, i + 2), k3 = argmax_key(v.w, i + 3);
+        k0 = k0 > k1 ? k0 : k1;
+        k2 = k2 > k3 ? k2 : k3;
+        k0 = k0 > k2 ? k0 : k2;
+        key = key > k0 ? key : k0;
     }
-    // NaN never compares greater; a row of NaN ends at its first visited index.
+    for (int i = head + 4 * n4 + threadIdx.x; i < V; i += blockDim.x) {
+        const unsigned long long k = argmax_key(row[i], i);
+        key = key > k ? key : k;
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+        key = key > other ? key : other;
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    if (lane == 0) best[warp] = key;
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (warp == 0) {
         const int n_warps = (blockDim.x + 31) >> 5;
-        for (int w = 1; w < n_warps; ++w) {
-            const float ov = best_v[w];
-            const int oi = best_i[w];
-            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        key = lane < n_warps ? best[lane] : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+            key = key > other ? key : other;
         }
-        out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+        // ~0: the row begins with NaN.  0 cannot be left over: element 0 is a number or has won.
+        if (lane == 0) out[blockIdx.x] = key == 0ull || key == ~0ull ? 0 : (int32_t)(0xffffffffu - (uint32_t)key);
     }
 }
 

@@ -17,7 +17,11 @@ def f64(t):
 
 SHAPES = [(1, 128, 64), (1, 4096, 4096), (3, 200, 96), (8, 320, 320), (16, 64, 256), (17, 136, 72),
           (33, 500, 1024), (64, 256, 64), (65, 256, 64), (128, 128, 128), (200, 330, 520), (256, 384, 2048),
-          (1000, 96, 320), (2048, 512, 4096)]
+          (1000, 96, 320), (2048, 512, 4096),
+          # CTA pairs: token counts and widths just past a tile border, widths that are no multiple of 256
+          (129, 136, 64), (257, 520, 136), (383, 1000, 192), (640, 1288, 72),
+          # few tokens: tiles of 88, 112 and 120 rows, a last tile that reaches past N, more tiles than SMs
+          (8, 12288, 256), (64, 16384, 128), (4, 50400, 128), (40, 2104, 320), (2, 19000, 64)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -72,7 +76,7 @@ def test_strided_input_and_row_independence():
     gemm_tc.check_status(x.device)
 
 
-@pytest.mark.parametrize("N,K", [(256, 4096), (4096, 4096), (520, 16384), (12288, 1024)])
+@pytest.mark.parametrize("N,K", [(256, 4096), (4096, 4096), (520, 16384), (12288, 1024), (12288, 4096), (1192, 2048)])
 def test_split_k_is_exact_and_does_not_depend_on_the_batch(N, K):
     """Few tokens and a long K: the product is cut along K over several CTAs whose partial tiles are
     added in slice order.  The result must match float64, be the same bits on every call, and a

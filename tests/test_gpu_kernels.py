@@ -206,6 +206,24 @@ def test_argmax_lowest_index_wins_ties():
     assert ops.argmax(x.cuda()).tolist() == [4999, 77, 0, 1023]
     y = torch.randn(9, 321, generator=torch.Generator().manual_seed(1))
     assert ops.argmax(y.cuda()).tolist() == [P.argmax_lowest(r.numpy()) for r in y]
+    # rows that start at every offset from a 16-byte boundary, widths with a ragged end
+    for width in (50400, 4099, 7, 3, 1):
+        z = torch.randn(5, width, generator=torch.Generator().manual_seed(width))
+        assert ops.argmax(z.cuda()).tolist() == [P.argmax_lowest(r.numpy()) for r in z], width
+
+
+def test_argmax_scans_like_a_strict_greater_than():
+    """NaN is never greater, so it is skipped unless the row begins with it; -0 equals +0; -inf rows give 0."""
+    nan, inf = float("nan"), float("inf")
+    rows = [
+        [1.0, nan, 5.0, nan, 5.0, 2.0, 0.0, 0.0],
+        [nan, 9.0, 1.0, 1.0, 1.0, 1.0, 1.0, 1.0],
+        [-0.0, 0.0, -1.0, -1.0, -1.0, -1.0, -1.0, -1.0],
+        [-inf] * 8,
+        [-3.0, -inf, inf, inf, 1.0, 1.0, 1.0, 1.0],
+    ]
+    x = torch.tensor(rows)
+    assert ops.argmax(x.cuda()).tolist() == [2, 0, 0, 0, 2]
 
 
 def test_repeat_penalty():
