@@ -20,6 +20,8 @@ SHAPES = [(1, 128, 64), (1, 4096, 4096), (3, 200, 96), (8, 320, 320), (16, 64, 2
           (1000, 96, 320), (2048, 512, 4096),
           # CTA pairs: token counts and widths just past a tile border, widths that are no multiple of 256
           (129, 136, 64), (257, 520, 136), (383, 1000, 192), (640, 1288, 72),
+          # CTA pairs: more tiles than pairs, with and without a whole round of them
+          (1000, 1288, 4096), (2048, 4096, 1024), (300, 9000, 1536),
           # few tokens: tiles of 88, 112 and 120 rows, a last tile that reaches past N, more tiles than SMs
           (8, 12288, 256), (64, 16384, 128), (4, 50400, 128), (40, 2104, 320), (2, 19000, 64)]
 
