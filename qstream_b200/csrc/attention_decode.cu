@@ -17,7 +17,6 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int WARPS = 4;
 constexpr int SPLIT = PAGE * WARPS;          // keys per CTA
-constexpr int UNROLL = 8;                    // 16-byte loads in flight per lane
 
 __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float (&f)[8]) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -28,10 +27,10 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float (&f)[8]) {
     }
 }
 
-// Lanes are grouped GS to a key (GS = the power of two >= dh / 8, at most 32); lane `c` of a group
+// Lanes are grouped GS to a key (GS = the power of two >= dh / 16, at most 32); lane `c` of a group
 // owns the 16-byte chunks c, c + GS, ... (NCH of them) of the head.  KPL = 32 / GS keys are
 // handled per warp instruction.
-template <int NCH>
+template <int NCH, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict__ q, size_t ldq,
                     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
@@ -255,15 +254,28 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
     QS_REQUIRE(T_tokens <= 65535 && n_heads <= 65535, "attention_decode: sizes exceed the grid");
     const int max_splits = (max_context + SPLIT - 1) / SPLIT;
     const int n_chunks = dh / 8;
+    // Two 16-byte chunks per lane: half as many lanes share a key, so a score costs one shuffle step
+    // less and a warp instruction covers twice the keys.  The grouping depends on the head size only
+    // (it fixes the order of the sums); how many loads a lane keeps in flight does not change a bit
+    // of the result and follows the size of the grid.
     int gs_log2 = 0;
-    while ((1 << gs_log2) < n_chunks && gs_log2 < 5) ++gs_log2;
-    const int nch = (n_chunks + 31) / 32;
+    while ((2 << gs_log2) < n_chunks && gs_log2 < 5) ++gs_log2;
+    const int nch = (n_chunks + (1 << gs_log2) - 1) >> gs_log2;
     dim3 grid(max_splits, n_heads, T_tokens);
     const size_t smem = (size_t)WARPS * dh * sizeof(float);
-#define GO(NCH) decode_split_kernel<NCH><<<grid, WARPS * 32, smem, stream>>>( \
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sm_count = 1;
+    }
+    const bool few_ctas = (long long)max_splits * n_heads * T_tokens <= 2LL * sm_count;
+#define GO(NCH, UNROLL) decode_split_kernel<NCH, UNROLL><<<grid, WARPS * 32, smem, stream>>>( \
         scratch, (const __nv_bfloat16*)q, (size_t)ldq, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
         page_table, max_pages, tok_slot, tok_pos, n_heads, n_kv_heads, dh, gs_log2, scale, window, max_splits, status)
-    if (nch == 1) GO(1); else GO(2);
+    if (nch == 1) GO(1, 8);
+    else if (few_ctas) GO(2, 8);
+    else GO(2, 4);
 #undef GO
     int rc = qs_check_launch("attention_decode");
     if (rc != QS_OK) return rc;
