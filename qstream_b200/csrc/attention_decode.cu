@@ -210,20 +210,22 @@ __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo,
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
     const int s_lo = first / SPLIT, s_hi = pos / SPLIT;
     const float* base = partial + ((size_t)t * n_heads + head) * max_splits * (dh + 2);
+    extern __shared__ float s_w[];                    // the splits' weights exp(m_s - M), computed once per block
     float M = -INFINITY;
     for (int s = s_lo; s <= s_hi; ++s) M = fmaxf(M, base[(size_t)s * (dh + 2) + dh]);
-    float L = 0.f;
-    for (int s = s_lo; s <= s_hi; ++s) {
+    for (int s = s_lo + threadIdx.x; s <= s_hi; s += blockDim.x) {
         const float ms = base[(size_t)s * (dh + 2) + dh];
-        if (ms != -INFINITY) L += base[(size_t)s * (dh + 2) + dh + 1] * expf(ms - M);
+        s_w[s - s_lo] = ms != -INFINITY ? expf(ms - M) : 0.f;
     }
+    __syncthreads();
+    float L = 0.f;
+    for (int s = s_lo; s <= s_hi; ++s)
+        if (s_w[s - s_lo] != 0.f) L += base[(size_t)s * (dh + 2) + dh + 1] * s_w[s - s_lo];
     const float inv = L > 0.f ? 1.0f / L : 0.f;
     for (int d = threadIdx.x; d < dh; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = s_lo; s <= s_hi; ++s) {
-            const float ms = base[(size_t)s * (dh + 2) + dh];
-            if (ms != -INFINITY) acc += base[(size_t)s * (dh + 2) + d] * expf(ms - M);
-        }
+        for (int s = s_lo; s <= s_hi; ++s)
+            if (s_w[s - s_lo] != 0.f) acc += base[(size_t)s * (dh + 2) + d] * s_w[s - s_lo];
         o[d] = __float2bfloat16_rn(acc * inv);
     }
 }
@@ -253,6 +255,7 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
     QS_REQUIRE(ldq % 8 == 0 && ((uintptr_t)q % 16) == 0, "attention_decode: queries must be 16-byte aligned rows");
     QS_REQUIRE(T_tokens <= 65535 && n_heads <= 65535, "attention_decode: sizes exceed the grid");
     const int max_splits = (max_context + SPLIT - 1) / SPLIT;
+    QS_REQUIRE(max_splits <= 12288, "attention_decode: a context of %d exceeds what the merge kernel holds (%d)", max_context, 12288 * SPLIT);
     const int n_chunks = dh / 8;
     // Two 16-byte chunks per lane: half as many lanes share a key, so a score costs one shuffle step
     // less and a warp instruction covers twice the keys.  The grouping depends on the head size only
@@ -279,7 +282,7 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
 #undef GO
     int rc = qs_check_launch("attention_decode");
     if (rc != QS_OK) return rc;
-    decode_merge_kernel<<<dim3(n_heads, T_tokens), dh >= 128 ? 128 : 64, 0, stream>>>(
+    decode_merge_kernel<<<dim3(n_heads, T_tokens), dh >= 128 ? 128 : 64, (size_t)max_splits * sizeof(float), stream>>>(
         (__nv_bfloat16*)out, (size_t)ldo, scratch, tok_slot, tok_pos, n_heads, dh, window, max_splits);
     return qs_check_launch("attention_decode merge");
 }
