@@ -678,28 +678,27 @@ int launch_stream(const void* W, const CUtensorMap& ma, const Epilogue& ep, int 
                                              cudaGetErrorString(e));
         configured = true;
     }
-    // One CTA per SM with a ring that fills its shared memory.  N is cut into whole tiles of equal height
-    // (8..128 rows), as many as fill the SMs an integral number of times, so that every SM streams its
-    // share of W and no partial sums are needed.  Where such tiles would still leave a tenth of the SMs
-    // idle (a narrow N), tiles of full height are dealt by k-blocks instead (stream-K) and the CTAs that
-    // share a tile add their partial tiles.  The dealing depends on N, K and the device only.
+    // One CTA per SM with a ring that fills its shared memory.  N is cut into tiles of equal height (a
+    // multiple of 8 rows, at most 128), as many as fill the SMs an integral number of times, so that every
+    // SM streams its share of W.  Tiles lower than about 64 rows pay more per k-block than they move, so a
+    // narrow N gets fewer, higher tiles, each cut along K into `splits` equal parts for as many CTAs: they
+    // add their partial tiles in the order of their k-ranges (the stream-K path of the kernel).  The dealing
+    // depends on N, K and the device only.
     const long long total_kb = (K + BK - 1) / BK;
     const long long waves = ((long long)N + (long long)BM * sm_count - 1) / ((long long)BM * sm_count);
-    long long rows = (N + waves * sm_count - 1) / (waves * sm_count);
+    long long splits = 1;
+    if (waves == 1 && ws && counters) {
+        splits = (long long)sm_count * 64 / N;
+        if (splits > total_kb / MIN_KB_PER_SPLIT) splits = total_kb / MIN_KB_PER_SPLIT;
+        if (splits < 1) splits = 1;
+    }
+    const long long slots = waves * sm_count / splits;           // tiles that run at a time
+    long long rows = (N + slots - 1) / slots;
     rows = (rows + 7) / 8 * 8;
     if (rows > BM) rows = BM;
-    long long tiles = (N + rows - 1) / rows;
-    long long G = tiles;
-    if (tiles * 10 < (tiles + sm_count - 1) / sm_count * sm_count * 9) {
-        const long long full_tiles = (N + BM - 1) / BM;
-        long long g = sm_count;
-        if (g > full_tiles * total_kb / MIN_KB_PER_SPLIT) g = full_tiles * total_kb / MIN_KB_PER_SPLIT;
-        if (ws && counters && g > full_tiles && full_tiles <= n_counters && g * 2 * BN * BM <= ws_floats) {
-            rows = BM;
-            tiles = full_tiles;
-            G = g;
-        }
-    }
+    const long long tiles = (N + rows - 1) / rows;
+    long long G = tiles * splits;
+    if (splits > 1 && (tiles > n_counters || G * 2 * BN * BM > ws_floats)) G = tiles;
     const int stage = (int)rows * BK * 2 + BN * BK * 2;
     int stages = (SMEM_MAX - 2048 - STREAM_PAD) / stage;
     if (stages > MAX_STREAM_STAGES) stages = MAX_STREAM_STAGES;
