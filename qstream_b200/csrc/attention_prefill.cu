@@ -85,8 +85,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     volatile uint32_t* aborted = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const TileInfo tile = tiles[blockIdx.x];
-    const int head = blockIdx.y;
+    // heads are the fast grid dimension and the tiles come longest first: CTAs start in order of falling
+    // work, so the last ones to start are the shortest (a causal tile's work grows with its position)
+    const TileInfo tile = tiles[blockIdx.y];
+    const int head = blockIdx.x;
     const int kvh = head / (n_heads / n_kv_heads);
     const int qpos_last = tile.qpos0 + tile.n_rows - 1;
     const int first_key = window > 0 ? max(0, tile.qpos0 - window + 1) : 0;
@@ -357,7 +359,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
                                              smem_bytes<NKC>(), cudaGetErrorString(e));
         configured = true;
     }
-    attention_prefill_kernel<NKC><<<dim3(n_tiles, n_heads), THREADS, smem_bytes<NKC>(), stream>>>(
+    attention_prefill_kernel<NKC><<<dim3(n_heads, n_tiles), THREADS, smem_bytes<NKC>(), stream>>>(
         mq, mk, mv, (__nv_bfloat16*)out, (size_t)ldo, tiles, page_table, max_pages, n_heads, n_kv_heads, dh,
         scale_log2, window, status);
     return qs_check_launch("attention_prefill");
@@ -381,7 +383,7 @@ QS_API int qs_attention_prefill(void* out, long long ldo, const void* q, long lo
     QS_REQUIRE(dh % 16 == 0 && dh >= 16 && dh <= 256, "attention_prefill: head size %d must be a multiple of 16 up to 256", dh);
     QS_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)out % 16) == 0,
                "attention_prefill: rows must be 16-byte aligned");
-    QS_REQUIRE(n_heads <= 65535, "attention_prefill: too many heads for the grid");
+    QS_REQUIRE(n_tiles <= 65535, "attention_prefill: %d tiles of queries are too many for the grid", n_tiles);
     CUtensorMap mq, mk, mv;
     int rc;
     if ((rc = make_map(&mq, q, T_tokens, (long long)n_heads * dh, ldq, BM)) != QS_OK) return rc;
