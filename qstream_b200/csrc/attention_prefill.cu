@@ -76,8 +76,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;
     uint64_t* v_full = k_full + STAGES;
-    uint64_t* kv_empty = v_full + STAGES;
-    uint64_t* s_full = kv_empty + STAGES;                // [2]
+    uint64_t* k_empty = v_full + STAGES;                  // a K tile is free once its Q K^T has completed,
+    uint64_t* v_empty = k_empty + STAGES;                 // a V tile once its P V has: the next keys load under the softmax
+    uint64_t* s_full = v_empty + STAGES;                  // [2]
     uint64_t* p_full = s_full + 2;                        // [2]
     uint64_t* p_free = p_full + 2;                        // [2]
     uint64_t* pv_done = p_free + 2;
@@ -97,7 +98,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1); }
         mbar_init(&s_full[0], 1);
         mbar_init(&s_full[1], 1);
         mbar_init(&p_full[0], BM);
@@ -125,21 +126,37 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             for (int c = 0; c < NKC; ++c)
                 tma_load_2d(q_smem + c * BM * KC * 2, &map_q, q_full, head * dh + c * KC, tile.row_start);
             const int32_t* pages = page_table + (size_t)tile.slot * max_pages;
-            for (int j = 0; j < n_blocks; ++j) {
-                const int st = j % STAGES;
-                const uint32_t phase = (j / STAGES) & 1;
-                if (!mbar_wait(&kv_empty[st], phase ^ 1)) { atomicExch(status, 111); *aborted = 1; break; }
+            auto tile_row = [&](int j) {
                 int page = pages[block_first + j];
                 if (page < 0) { atomicExch(status, 3); page = 0; }       // still fill the stage so nobody waits for it
-                const int row = (page * n_kv_heads + kvh) * BN;
+                return (page * n_kv_heads + kvh) * BN;
+            };
+            auto load_k = [&](int j) -> bool {
+                const int st = j % STAGES;
+                if (!mbar_wait(&k_empty[st], ((j / STAGES) & 1) ^ 1)) { atomicExch(status, 111); *aborted = 1; return false; }
+                const int row = tile_row(j);
                 uint8_t* k_tile = kv_smem + (size_t)st * 2 * KV_TILE;
-                uint8_t* v_tile = k_tile + KV_TILE;
                 mbar_expect_tx(&k_full[st], KV_TILE);
 #pragma unroll
                 for (int c = 0; c < NKC; ++c) tma_load_2d(k_tile + c * BN * KC * 2, &map_k, &k_full[st], c * KC, row);
+                return true;
+            };
+            auto load_v = [&](int j) -> bool {
+                const int st = j % STAGES;
+                if (!mbar_wait(&v_empty[st], ((j / STAGES) & 1) ^ 1)) { atomicExch(status, 110); *aborted = 1; return false; }
+                const int row = tile_row(j);
+                uint8_t* v_tile = kv_smem + (size_t)st * 2 * KV_TILE + KV_TILE;
                 mbar_expect_tx(&v_full[st], KV_TILE);
 #pragma unroll
                 for (int c = 0; c < NKC; ++c) tma_load_2d(v_tile + c * BN * KC * 2, &map_v, &v_full[st], c * KC, row);
+                return true;
+            };
+            // in the order in which the slots come free: keys of block j + 1 (after Q K^T of block j + 1 - STAGES),
+            // then values of block j (after P V of block j - STAGES)
+            bool ok = load_k(0);
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                if (j + 1 < n_blocks) ok = load_k(j + 1);
+                if (ok) ok = load_v(j);
             }
         }
     } else if (warp == 1) {
@@ -163,6 +180,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                              smem_desc_sw128(ka + c * BN * KC * 2 + kk * 32), idesc_qk, k != 0);
                 }
                 mma_commit(&s_full[j & 1]);
+                mma_commit(&k_empty[st]);
                 return true;
             };
             if (ok) ok = issue_qk(0);
@@ -182,7 +200,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     mma_bf16(tmem_base + O_COL, smem_desc_sw128(pa + k * 32),
                              smem_desc_sw128_mn(va + k * 2048, BN * KC * 2, 1024), idesc_pv, (j | k) != 0);
                 }
-                mma_commit(&kv_empty[st]);
+                mma_commit(&v_empty[st]);
                 mma_commit(&p_free[j & 1]);
                 mma_commit(pv_done);
             }
