@@ -35,7 +35,7 @@ namespace {
 constexpr int BM = 128;          // query rows per CTA = TMEM lanes
 constexpr int BN = 64;           // keys per block = one cache page
 constexpr int KC = 64;           // columns of one swizzled tile (128 bytes of bfloat16)
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;      // producer warp, MMA warp, eight softmax warps
 constexpr float RESCALE_THRESHOLD = 8.0f;        // log2 units
 
 struct TileInfo { int row_start, n_rows, qpos0, slot; };
@@ -47,12 +47,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// The value rounded up (toward +inf) to one whose low 16 bits are zero; -inf and +inf stay.
+__device__ __forceinline__ float round_up_16(float x) {
+    const uint32_t u = __float_as_uint(x);
+    if ((u & 0xffffu) == 0u) return x;
+    return __uint_as_float(x > 0.f ? (u + 0x10000u) & 0xffff0000u : u & 0xffff0000u);
+}
+
 template <int NKC> constexpr int kv_stages() { return NKC == 4 ? 2 : (NKC == 3 ? 3 : 4); }
 template <int NKC> constexpr int q_bytes() { return BM * KC * 2 * NKC; }
 template <int NKC> constexpr int kv_tile_bytes() { return BN * KC * 2 * NKC; }      // one of K or V
 constexpr int P_BYTES = BM * BN * 2;            // one buffer of softmax weights; there are two
 template <int NKC> constexpr int smem_bytes() {
-    return q_bytes<NKC>() + 2 * kv_stages<NKC>() * kv_tile_bytes<NKC>() + 2 * P_BYTES + 1024 + 512;
+    return q_bytes<NKC>() + 2 * kv_stages<NKC>() * kv_tile_bytes<NKC>() + 2 * P_BYTES + 1024 + 512 + 4 * BM * 2;
 }
 
 template <int NKC>
@@ -84,6 +91,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t* pv_done = p_free + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
     volatile uint32_t* aborted = tmem_slot + 1;
+    uint16_t* row_max = reinterpret_cast<uint16_t*>(bars + 64);    // [2 buffers][2 halves][BM], 512 bytes behind the barriers
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // heads are the fast grid dimension and the tiles come longest first: CTAs start in order of falling
@@ -101,8 +109,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1); }
         mbar_init(&s_full[0], 1);
         mbar_init(&s_full[1], 1);
-        mbar_init(&p_full[0], BM);
-        mbar_init(&p_full[1], BM);
+        mbar_init(&p_full[0], 2 * BM);
+        mbar_init(&p_full[1], 2 * BM);
         mbar_init(&p_free[0], 1);
         mbar_init(&p_free[1], 1);
         mbar_init(pv_done, 1);
@@ -211,7 +219,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
     } else {
         // ------------------------------------------------------------------ softmax and epilogue
+        // Eight warps, two threads per query row: warps 2..5 take key columns 0..31 of a block, warps 6..9
+        // columns 32..63 (a warp may touch the TMEM lanes 32 (warp % 4) .. +31, so both see the same rows).
+        // The two threads of a row exchange their block maxima through shared memory (one named barrier per
+        // block), keep partial row sums that are added at the end, and share the columns of O between them.
+        // No thread leaves the loop early: a wait that ran out clears `ok` and the thread goes on to every
+        // barrier without touching anything.
         const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = quad * 32 + lane;
         const bool valid = r < tile.n_rows;
         const int qpos = valid ? tile.qpos0 + r : -1;
@@ -220,44 +235,49 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_blocks; ++j) {
-            if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(status, 116); ok = false; break; }
-            if (*aborted) { ok = false; break; }
+            if (ok && !mbar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(status, 116); ok = false; }
+            if (*aborted) ok = false;
             tc_fence_after_sync();
-            uint32_t raw[2][32];
-            tmem_load_32x32(tmem_base + lane_base + (uint32_t)((j & 1) * BN), raw[0]);
-            tmem_load_32x32(tmem_base + lane_base + (uint32_t)((j & 1) * BN + 32), raw[1]);
+            uint32_t raw[32];
+            tmem_load_32x32(tmem_base + lane_base + (uint32_t)((j & 1) * BN + half * 32), raw);
             tmem_load_wait();
-            const int key0 = (block_first + j) * BN;
-            const bool all_visible = key0 + BN - 1 <= qpos && key0 >= lo;
-            // raw scores stay in `raw`; masked ones become -inf.  The maximum is taken over four independent
-            // chains (the thread has no other warp to hide a 64-long dependent chain behind).
+            const int key0 = (block_first + j) * BN + half * 32;
+            const bool all_visible = key0 + 31 <= qpos && key0 >= lo;
+            // raw scores stay in `raw`; masked ones become -inf.  The maximum is taken over four independent chains.
             if (!all_visible) {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) {
+                for (int c = 0; c < 32; ++c) {
                     const int key = key0 + c;
-                    if (key > qpos || key < lo) raw[c >> 5][c & 31] = 0xff800000u;       // -inf
+                    if (key > qpos || key < lo) raw[c] = 0xff800000u;       // -inf
                 }
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < BN; c += 4) {
+            for (int c = 0; c < 32; c += 4) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(raw[(c + u) >> 5][(c + u) & 31]));
+                for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(raw[c + u]));
             }
-            const float bmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;    // scale_log2 > 0
+            // The maximum only steadies the exponentials: any common value at or above the true one serves.  The
+            // two threads exchange theirs rounded up to 16 bits (half the shared memory) and both use the
+            // larger of the two rounded values.
+            const float mine = round_up_16(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
+            uint16_t* xch = row_max + (j & 1) * 2 * BM;   // two buffers: block j + 2 writes only after everyone passed barrier j + 1
+            xch[half * BM + r] = (uint16_t)(__float_as_uint(mine) >> 16);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float theirs = __uint_as_float((uint32_t)xch[(half ^ 1) * BM + r] << 16);
+            const float bmax = fmaxf(mine, theirs) * scale_log2;                      // scale_log2 > 0
             // Two buffers of weights: this block's buffer is free once the P V of block j - 2 has completed
             // (a barrier per buffer), so these exponentials run under the P V of block j - 1.
-            if (j > 1 && !mbar_wait(&p_free[j & 1], ((j >> 1) - 1) & 1)) { atomicExch(status, 117); ok = false; break; }
-            const bool grow = bmax > m + RESCALE_THRESHOLD || (m == -INFINITY && bmax > -INFINITY);
+            if (ok && j > 1 && !mbar_wait(&p_free[j & 1], ((j >> 1) - 1) & 1)) { atomicExch(status, 117); ok = false; }
+            const bool grow = ok && (bmax > m + RESCALE_THRESHOLD || (m == -INFINITY && bmax > -INFINITY));
             if (__any_sync(0xffffffffu, grow)) {         // tcgen05.ld/st are warp-wide: the whole warp goes
                 const float m_new = grow ? bmax : m;
                 const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);     // 1 where the row keeps its scale
                 if (j > 0) {
-                    // O may only be touched between two P V products
-                    if (!mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(status, 119); ok = false; break; }
+                    // O may only be touched between two P V products; the row's two threads take every other chunk
+                    if (ok && !mbar_wait(pv_done, (j - 1) & 1)) { atomicExch(status, 119); ok = false; }
                     tc_fence_after_sync();
-                    for (int c = 0; c < NKC * 2; ++c) {
-                        if (c * 32 >= dh) break;
+                    for (int c = half; c * 32 < dh; c += 2) {
                         uint32_t o[32];
                         tmem_load_32x32(tmem_base + lane_base + O_COL + (uint32_t)(c * 32), o);
                         tmem_load_wait();
@@ -272,36 +292,44 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             // P = exp2(s * scale - m) (one FMA and one ex2 per score), rounded to bfloat16 and written in the
             // swizzled K-major layout; the row sum is taken in 32-bit over two independent chains.
-            uint8_t* prow = p_smem + (j & 1) * P_BYTES + (size_t)r * 128;
-            const float neg_m = m == -INFINITY ? -INFINITY : -m;          // a row with no visible key so far: all weights 0
-            float ps0 = 0.f, ps1 = 0.f;
+            if (ok) {
+                uint8_t* prow = p_smem + (j & 1) * P_BYTES + (size_t)r * 128;
+                const float neg_m = m == -INFINITY ? -INFINITY : -m;          // a row with no visible key so far: all weights 0
+                float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                uint32_t w[4];
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint32_t w[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int c = ch * 8 + 2 * i;
-                    const float sa = __uint_as_float(raw[c >> 5][c & 31]), sb = __uint_as_float(raw[(c + 1) >> 5][(c + 1) & 31]);
-                    const float a = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sa, scale_log2, neg_m));
-                    const float b = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sb, scale_log2, neg_m));
-                    ps0 += a;
-                    ps1 += b;
-                    const __nv_bfloat162 pb = __floats2bfloat162_rn(a, b);
-                    w[i] = *reinterpret_cast<const uint32_t*>(&pb);
+                    for (int i = 0; i < 4; ++i) {
+                        const int c = ch * 8 + 2 * i;
+                        const float sa = __uint_as_float(raw[c]), sb = __uint_as_float(raw[c + 1]);
+                        const float a = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sa, scale_log2, neg_m));
+                        const float b = neg_m == -INFINITY ? 0.f : fast_exp2(fmaf(sb, scale_log2, neg_m));
+                        ps0 += a;
+                        ps1 += b;
+                        const __nv_bfloat162 pb = __floats2bfloat162_rn(a, b);
+                        w[i] = *reinterpret_cast<const uint32_t*>(&pb);
+                    }
+                    *reinterpret_cast<uint4*>(prow + (((half * 4 + ch) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                l += ps0 + ps1;
+                fence_proxy_async_smem();
+                tc_fence_before_sync();
+                mbar_arrive(&p_full[j & 1]);
             }
-            l += ps0 + ps1;
-            fence_proxy_async_smem();
-            tc_fence_before_sync();
-            mbar_arrive(&p_full[j & 1]);
         }
         if (ok && !mbar_wait(pv_done, (n_blocks - 1) & 1)) { atomicExch(status, 118); ok = false; }
+        // the row's sum: the two partial sums in the order of their columns
+        float* lsum = reinterpret_cast<float*>(p_smem);   // the weights' buffers are free now
+        asm volatile("bar.sync 1, 256;" ::: "memory");    // every thread has seen the last P V complete (or given up)
+        lsum[half * BM + r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float l_all = lsum[r] + lsum[BM + r];
         if (ok && !*aborted) {
             tc_fence_after_sync();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             __nv_bfloat16* orow = out + (size_t)(tile.row_start + r) * ldo + (size_t)head * dh;
-            for (int c = 0; c * 32 < dh; ++c) {
+            for (int c = half; c * 32 < dh; c += 2) {
                 uint32_t o[32];
                 tmem_load_32x32(tmem_base + lane_base + O_COL + (uint32_t)(c * 32), o);
                 tmem_load_wait();
