@@ -100,7 +100,7 @@ class ClockSampler:
 
 def reference_arm():
     # QStream is a CPU-only C program without a Python package (no setup.py or pyproject.toml), so
-    # `pip install ... /root/reference` has nothing to install; its converter cannot read a GPT-J
+    # a `pip install` of its source tree has nothing to install; its converter cannot read a GPT-J
     # folder and its engine has no GPT-J forward pass or unquantized weights.
     print(json.dumps({"impl": "reference",
                       "unavailable": "QStream is a CPU-only C engine with no Python package to install; its "
