@@ -222,10 +222,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
 // ----------------------------------------------------------------------------- persistent kernel on CTA pairs
 
-constexpr int PAIR_STAGE = BM * BK * 2 * 2;           // per CTA and stage: 128 rows of A and 128 rows of W, 64 wide
-constexpr int PAIR_STAGES = SMEM_BUDGET_BIG / PAIR_STAGE;
-constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE + 1024 + 512;
-constexpr int PAIR_BN = 256;
+// per CTA and stage: 128 rows of A and its half of the PAIR_BN rows of W, 64 wide
+template <int PAIR_BN> constexpr int pair_stage() { return BM * BK * 2 + (PAIR_BN / 2) * BK * 2; }
+template <int PAIR_BN> constexpr int pair_stages() { return SMEM_BUDGET_BIG / pair_stage<PAIR_BN>(); }
+template <int PAIR_BN> constexpr int pair_smem() { return pair_stages<PAIR_BN>() * pair_stage<PAIR_BN>() + 1024 + 512; }
 
 // Like wait_or_abort, and it also gives up when any CTA of the grid has reported a failure.
 __device__ __forceinline__ bool wait_or_abort_grid(uint64_t* bar, uint32_t parity, volatile uint32_t* aborted,
@@ -237,17 +237,21 @@ __device__ __forceinline__ bool wait_or_abort_grid(uint64_t* bar, uint32_t parit
     return false;
 }
 
-// Two CTAs on neighbouring SMs work on one 256 x 256 output tile with tcgen05.mma.cta_group::2: each CTA
-// loads its own 128 rows of A and its own half (128 rows) of the W tile - half the shared-memory traffic
-// per flop of the single-CTA kernel - and holds its 128 x 256 half of the accumulator in its TMEM.  The
+// Two CTAs on neighbouring SMs work on one 256 x PAIR_BN output tile (PAIR_BN = 256, or 192 where that wastes
+// less of the last round of tiles) with tcgen05.mma.cta_group::2: each CTA
+// loads its own 128 rows of A and its own half of the W tile - half the shared-memory traffic
+// per flop of the single-CTA kernel - and holds its 128 x PAIR_BN half of the accumulator in its TMEM.  The
 // even CTA (the leader) issues the MMAs for both; all TMA bytes of a stage are counted on the leader's
 // barrier; tcgen05.commit tells both CTAs when a stage or an accumulator may be used again; the other
 // CTA's epilogue warps signal the leader across the cluster.  No load uses multicast.
+template <int PAIR_BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const Epilogue ep, const int K, const int m_pairs, const int n_tiles,
                     int32_t* __restrict__ status) {
-    constexpr uint32_t TMEM_COLS = 2 * PAIR_BN;
+    constexpr int PAIR_STAGE = pair_stage<PAIR_BN>();
+    constexpr int PAIR_STAGES = pair_stages<PAIR_BN>();
+    constexpr uint32_t TMEM_COLS = 512;             // two accumulators of PAIR_BN columns; a power of two
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE);
@@ -712,39 +716,47 @@ int launch_stream(const void* W, const CUtensorMap& ma, const Epilogue& ep, int 
     return qs_check_launch("gemm_tc stream");
 }
 
-// The CTA-pair kernel as a cluster launch; `*launched` tells whether this device can run it at all.
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const Epilogue& ep, int M, int N, int K,
-                int32_t* status, cudaStream_t stream, bool* launched) {
+// The CTA-pair kernel as a cluster launch; 0 clusters means this device cannot run it at all.
+template <int PAIR_BN>
+int pair_max_clusters() {
     static int state = 0;                 // 0 = not probed, 1 = usable, -1 = not usable
     static int max_clusters = 0;
-    *launched = false;
     if (state == 0) {
         state = -1;
-        if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM) == cudaSuccess) {
+        if (cudaFuncSetAttribute(gemm_tc_pair_kernel<PAIR_BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 pair_smem<PAIR_BN>()) == cudaSuccess) {
             cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(2); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = PAIR_SMEM;
+            cfg.gridDim = dim3(2); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = pair_smem<PAIR_BN>();
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
             cfg.attrs = attr; cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel, &cfg) == cudaSuccess && n > 0) { max_clusters = n; state = 1; }
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<PAIR_BN>, &cfg) == cudaSuccess && n > 0) { max_clusters = n; state = 1; }
         }
         cudaGetLastError();
     }
-    if (state != 1) return QS_OK;
+    return state == 1 ? max_clusters : 0;
+}
+
+template <int PAIR_BN>
+int launch_pair(const CUtensorMap& ma, const void* W, const Epilogue& ep, int M, int N, int K,
+                int32_t* status, cudaStream_t stream) {
+    const int max_clusters = pair_max_clusters<PAIR_BN>();
+    CUtensorMap mw;
+    int rc = tensor_map(&mw, W, N, K, K, PAIR_BN / 2);
+    if (rc != QS_OK) return rc;
     const int m_pairs = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + PAIR_BN - 1) / PAIR_BN;
     const long long total = (long long)m_pairs * n_tiles;
     const int clusters = (int)(total < max_clusters ? total : max_clusters);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = PAIR_SMEM; cfg.stream = stream;
+    cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = pair_smem<PAIR_BN>(); cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, ma, mw, ep, K, m_pairs, n_tiles, status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<PAIR_BN>, ma, mw, ep, K, m_pairs, n_tiles, status);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc pair: %s", cudaGetErrorString(e));
-    *launched = true;
     return qs_check_launch("gemm_tc pair");
 }
 
@@ -793,11 +805,18 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
     if (M > 64) {
         QS_REQUIRE((M + BM - 1) / BM <= 65535 * 1 && (N + 127) / 128 <= 65535, "gemm_tc: sizes exceed the grid");
         if ((rc = tensor_map(&ma, A, M, K, lda, BM)) != QS_OK) return rc;
-        if (M > BM && N > 128) {                     // enough rows for a pair of CTAs: 256 x 256 tiles
-            if ((rc = tensor_map(&mw, W, N, K, K, BM)) != QS_OK) return rc;
-            bool launched = false;
-            rc = launch_pair(ma, mw, ep, M, N, K, status, stream, &launched);
-            if (rc != QS_OK || launched) return rc;
+        if (M > BM && N > 128) {                     // enough rows for a pair of CTAs: tiles of 256 rows
+            const int c256 = pair_max_clusters<256>(), c192 = pair_max_clusters<192>();
+            if (c256 > 0) {
+                // Tiles 192 wide where the rounds over the CTA pairs then cost less, a narrower tile's lower
+                // efficiency (measured: about a tenth) included: 384 tiles of 256 are 6 rounds over 74 pairs, the same
+                // matrix in 512 tiles of 192 is 7 rounds of three quarters the length.
+                const long long m_pairs = (M + 2 * BM - 1) / (2 * BM);
+                const long long r256 = (m_pairs * ((N + 255) / 256) + c256 - 1) / c256 * 256;
+                const long long r192 = c192 > 0 ? (m_pairs * ((N + 191) / 192) + c192 - 1) / c192 * 192 : r256;
+                if (r192 * 112 < r256 * 100) return launch_pair<192>(ma, W, ep, M, N, K, status, stream);
+                return launch_pair<256>(ma, W, ep, M, N, K, status, stream);
+            }
         }
         const int bn = N > 128 ? 256 : 128;
         if ((rc = tensor_map(&mw, W, N, K, K, bn)) != QS_OK) return rc;
