@@ -7,10 +7,10 @@
 // warps 2..5 = epilogue (warp w reads TMEM lanes 32 * (w % 4) .. +31).
 //
 // Two kernels:
-//   many tokens (M > 64): rows of A on the MMA's M side, rows of W on its N side; a persistent CTA per SM
+//   many tokens (M > 128): rows of A on the MMA's M side, rows of W on its N side; a persistent CTA per SM
 //       walks over 128 x 256 output tiles with two TMEM accumulators, so the epilogue of one tile runs
 //       under the main loop of the next;
-//   few tokens (M <= 64): rows of W on the M side and the tokens on the N side (16, 32 or 64), so no
+//   few tokens (M <= 128): rows of W on the M side and the tokens on the N side (16, 32, 64 or 128), so no
 //       tensor-core row is spent on padding; one CTA per SM streams whole tiles of W, or - for a narrow
 //       N - an even share of all k-blocks (stream-K) with a deterministic reduction of partial tiles.
 // Each output element is accumulated over K in ascending k (in one TMEM cell, or in a fixed sequence of
@@ -787,7 +787,7 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const Epilog
 // A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16 contiguous; C: [M, N] bfloat16 or float32.
 // res1/res2: bfloat16 [M, N] with row stride ldr, or null.  status: device int32 that receives a
 // non-zero code if a bounded wait inside the kernel ran out.
-// ws / counters: scratch for split-K in the weight-streaming arrangement (M <= 64): `ws_floats` floats
+// ws / counters: scratch for split-K in the weight-streaming arrangement (M <= 128): `ws_floats` floats
 // and `n_counters` int32 that are ZERO before the first call (the kernel leaves them zero).  Without
 // them (null) the product runs unsplit.  Calls that share the scratch must not overlap on the GPU.
 QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const void* bias, int bias_dtype, int act,
@@ -802,7 +802,7 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
     Epilogue ep{C, c_dtype, ldc, bias, bias_dtype, act, (const __nv_bfloat16*)res1, (const __nv_bfloat16*)res2, ldr, M, N};
     CUtensorMap ma, mw;
     int rc;
-    if (M > 64) {
+    if (M > 128) {
         QS_REQUIRE((M + BM - 1) / BM <= 65535 * 1 && (N + 127) / 128 <= 65535, "gemm_tc: sizes exceed the grid");
         if ((rc = tensor_map(&ma, A, M, K, lda, BM)) != QS_OK) return rc;
         if (M > BM && N > 128) {                     // enough rows for a pair of CTAs: tiles of 256 rows
@@ -823,9 +823,10 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
         if (bn == 256) return launch_persistent<256>(ma, mw, ep, M, N, K, status, stream);
         return launch_persistent<128>(ma, mw, ep, M, N, K, status, stream);
     }
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     if ((rc = tensor_map(&ma, A, M, K, lda, bn)) != QS_OK) return rc;
     if (bn == 16) return launch_stream<16>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
     if (bn == 32) return launch_stream<32>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    return launch_stream<64>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    if (bn == 64) return launch_stream<64>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    return launch_stream<128>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
 }

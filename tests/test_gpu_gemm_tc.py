@@ -23,7 +23,9 @@ SHAPES = [(1, 128, 64), (1, 4096, 4096), (3, 200, 96), (8, 320, 320), (16, 64, 2
           # CTA pairs: more tiles than pairs, with and without a whole round of them
           (1000, 1288, 4096), (2048, 4096, 1024), (300, 9000, 1536),
           # few tokens: tiles of 88, 112 and 120 rows, a last tile that reaches past N, more tiles than SMs
-          (8, 12288, 256), (64, 16384, 128), (4, 50400, 128), (40, 2104, 320), (2, 19000, 64)]
+          (8, 12288, 256), (64, 16384, 128), (4, 50400, 128), (40, 2104, 320), (2, 19000, 64),
+          # 65 to 128 tokens still stream the weights (128 tokens on the N side), with and without cuts along K
+          (100, 12288, 256), (128, 2104, 320), (96, 520, 16384), (127, 4096, 4096)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -38,7 +40,7 @@ def test_plain_product(M, N, K):
     np.testing.assert_allclose(f64(got), ref, atol=2e-3, rtol=2e-3)   # float32 accumulation of exact products
 
 
-@pytest.mark.parametrize("M", [5, 40, 300])
+@pytest.mark.parametrize("M", [5, 40, 100, 300])
 @pytest.mark.parametrize("act", [None, "gelu_new", "gelu"])
 def test_epilogue(M, act):
     N, K = 264, 136
