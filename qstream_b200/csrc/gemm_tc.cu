@@ -424,7 +424,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     // whatever lies behind the slot and are never stored.
     const int STAGE = tile_rows * BK * 2 + BN * BK * 2;
     constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    constexpr int CH = BN < 32 ? 16 : 32;
+    constexpr int CH = 16;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -525,6 +525,11 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         const int quad = warp & 3;
         const int r = quad * 32 + lane;                   // TMEM lane = output feature within the tile
         grid_dep_wait();                                  // residuals, outputs and the workspace belong to earlier kernels until now
+        // 16-byte stores and residual loads need features in whole groups of eight and aligned rows
+        const bool vec_ok = (ep.N % 8) == 0 && (ep.ldc % 8) == 0 &&
+                            ((uintptr_t)ep.C % (ep.c_dtype == QS_BF16 ? 16 : 32)) == 0 &&
+                            (!ep.res1 || ((ep.ldr % 8) == 0 && ((uintptr_t)ep.res1 % 16) == 0)) &&
+                            (!ep.res2 || ((ep.ldr % 8) == 0 && ((uintptr_t)ep.res2 % 16) == 0));
         int seg = 0, tile = tile_begin, kb0 = kb_begin, left = count;
         for (; left > 0; ++seg, ++tile, kb0 = 0) {
             const int n = min(total_kb - kb0, left);
@@ -536,17 +541,85 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
             auto load_acc = [&](int c, float (&v)[CH]) {
                 uint32_t raw[CH];
-                if constexpr (CH == 32) tmem_load_32x32(tacc + c * CH, raw); else tmem_load_32x16(tacc + c * CH, raw);
+                tmem_load_32x16(tacc + c * CH, raw);
                 tmem_load_wait();
 #pragma unroll
                 for (int j = 0; j < CH; ++j) v[j] = __uint_as_float(raw[j]);
             };
+            // This thread holds one output feature for CH tokens.  A warp's store of one token is 64 bytes of
+            // 2-byte elements, and such stores cost about 200 cycles each (86 with 4-byte elements), one after the
+            // other: 64 tokens took 13,000 cycles.  So, where the layout allows 16-byte stores, groups of eight
+            // lanes transpose 8 x 8 blocks by shuffles: a lane then holds eight neighbouring features of one
+            // token and stores them at once.  Bias and activation come before the transpose (they go by
+            // feature), residuals and the one rounding after it.
+            const float bias_v = (feat < ep.N && ep.bias) ? load_as_f32(ep.bias, ep.bias_dtype, feat) : 0.f;
+            const int sub = lane & 7;
+            const int group_row = r - sub;                                    // the group's first TMEM lane
+            const int group_feat = tile * tile_rows + group_row;
+            const bool group_ok = group_row < tile_rows && group_feat < ep.N;  // all eight or none (multiples of 8)
             auto emit = [&](int c, const float (&v)[CH]) {
-                if (feat < ep.N) {
+                const int m0 = c * CH;
+                if (vec_ok) {
+                    float y[CH];
 #pragma unroll
-                    for (int j = 0; j < CH; ++j) {
-                        const int m = c * CH + j;
-                        if (m < ep.M) store_out(ep, m, feat, v[j]);
+                    for (int j = 0; j < CH; ++j) y[j] = apply_activation_fast(v[j] + bias_v, ep.act);
+#pragma unroll
+                    for (int blk = 0; blk < CH / 8; ++blk) {
+#pragma unroll
+                        for (int s = 4; s >= 1; s >>= 1) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                if (i & s) continue;
+                                float& lo = y[blk * 8 + i];
+                                float& hi = y[blk * 8 + (i | s)];
+                                const float got = __shfl_xor_sync(0xffffffffu, (lane & s) ? lo : hi, s);
+                                if (lane & s) lo = got; else hi = got;
+                            }
+                        }
+                        const int m = m0 + blk * 8 + sub;                      // y[blk * 8 + i] = feature group_feat + i of token m
+                        if (!group_ok || m >= ep.M) continue;
+                        float x[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) x[i] = y[blk * 8 + i];
+                        if (ep.res1) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + group_feat);
+                            const uint32_t w4[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) { x[2 * i] += __uint_as_float(w4[i] << 16); x[2 * i + 1] += __uint_as_float(w4[i] & 0xffff0000u); }
+                        }
+                        if (ep.res2) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res2 + (size_t)m * ep.ldr + group_feat);
+                            const uint32_t w4[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) { x[2 * i] += __uint_as_float(w4[i] << 16); x[2 * i + 1] += __uint_as_float(w4[i] & 0xffff0000u); }
+                        }
+                        if (ep.c_dtype == QS_BF16) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const __nv_bfloat162 pb = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+                                o[i] = *reinterpret_cast<const uint32_t*>(&pb);
+                            }
+                            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(ep.C) + (size_t)m * ep.ldc + group_feat) =
+                                make_uint4(o[0], o[1], o[2], o[3]);
+                        } else {
+                            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(ep.C) + (size_t)m * ep.ldc + group_feat);
+                            dst[0] = make_float4(x[0], x[1], x[2], x[3]);
+                            dst[1] = make_float4(x[4], x[5], x[6], x[7]);
+                        }
+                    }
+                    return;
+                }
+                if (feat >= ep.N) return;
+                const __nv_bfloat16* r1 = ep.res1 ? ep.res1 + (size_t)m0 * ep.ldr + feat : nullptr;
+                const __nv_bfloat16* r2 = ep.res2 ? ep.res2 + (size_t)m0 * ep.ldr + feat : nullptr;
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                    if (m0 + j < ep.M) {
+                        float x = apply_activation_fast(v[j] + bias_v, ep.act);
+                        if (r1) x += __bfloat162float(r1[(size_t)j * ep.ldr]);
+                        if (r2) x += __bfloat162float(r2[(size_t)j * ep.ldr]);
+                        store_from_f32(ep.C, ep.c_dtype, (size_t)(m0 + j) * ep.ldc + feat, x);
                     }
                 }
             };
