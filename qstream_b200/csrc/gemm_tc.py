@@ -34,10 +34,25 @@ N_COUNTERS = 1 << 16
 _scratch = {}
 
 
+scratch_slot = 0                # which set of scratch the next products use (see `second_scratch`)
+
+
+class second_scratch:
+    """Products launched inside this context use a second set of scratch: for a stream that runs
+    beside the main one (products on one stream run in order and may share a set; two streams may not)."""
+
+    def __enter__(self):
+        global scratch_slot
+        self.before, scratch_slot = scratch_slot, 1
+
+    def __exit__(self, *exc):
+        global scratch_slot
+        scratch_slot = self.before
+
+
 def scratch(device):
-    """Per-device scratch of the split-K reduction: partial tiles and zeroed arrival counters.
-    Shared by all calls on the device, which run on one stream."""
-    key = (device.type, device.index)
+    """Per-device scratch of the split-K reduction: partial tiles and zeroed arrival counters."""
+    key = (device.type, device.index, scratch_slot)
     if key not in _scratch:
         _scratch[key] = (torch.empty(WS_FLOATS, dtype=torch.float32, device=device),
                          torch.zeros(N_COUNTERS, dtype=torch.int32, device=device))

@@ -60,7 +60,7 @@ class DecodeGraph:
     def capture(self) -> None:
         from ..csrc import ops
         eng = self._engine()
-        ctx = StepContext(self.batch, eng.cache, eng.status)
+        ctx = StepContext(self.batch, eng.cache, eng.status, eng.side_stream)
         stream = torch.cuda.Stream(device=eng.device)
         stream.wait_stream(torch.cuda.current_stream(eng.device))
         with torch.cuda.stream(stream):
@@ -74,7 +74,9 @@ class DecodeGraph:
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(self.graph):
+            # the main chain of kernels is captured with a higher priority than the side stream's product,
+            # which then only fills what the chain leaves idle
+            with torch.cuda.graph(self.graph, stream=torch.cuda.Stream(device=eng.device, priority=-1)):
                 self.logits = eng.model.forward(ctx)
         finally:
             if gc_was_on:

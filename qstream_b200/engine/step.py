@@ -49,10 +49,12 @@ class StepBatch:
 class StepContext:
     """What a part may touch during a step."""
 
-    def __init__(self, batch: StepBatch, cache: SequenceCache, status: torch.Tensor):
+    def __init__(self, batch: StepBatch, cache: SequenceCache, status: torch.Tensor, side_stream=None):
         self.batch = batch
         self.cache = cache
         self.status = status
+        # a second CUDA stream for work that does not depend on the mixer (None: everything in order)
+        self.side_stream = side_stream
 
     def kv(self, cache_id: int):
         return self.cache.view(cache_id)
@@ -91,6 +93,8 @@ class Engine:
         self._check_budget(kv_needs, max_tokens)
         self.cache = SequenceCache(kv_needs, state_needs, max_tokens, max_batch, ctx, self.dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # decode steps run the feed-forward's first product beside the attention kernels
+        self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.use_graphs = use_graphs and self.device.type == "cuda"
         self._graphs = {}
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else None
@@ -198,7 +202,7 @@ class Engine:
         batch = self.build_batch(slots, tokens, want)
         if batch.n_tokens == 0:
             return None
-        logits = self.model.forward(StepContext(batch, self.cache, self.status))
+        logits = self.model.forward(StepContext(batch, self.cache, self.status, self.side_stream))
         self.cache.commit(batch.slots, batch.new_tokens)
         return logits
 

@@ -20,3 +20,32 @@ def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, 
         if gemm_tc.takes(x, weight):
             return gemm_tc.linear(x, weight, bias, activation, residuals, out_dtype, out)
     return ops.linear_simt(x, weight, bias, activation, residuals, out_dtype, out)
+
+
+class beside_main_stream:
+    """Enter a second CUDA stream that has waited for everything the current stream holds so far; products
+    inside use a scratch of their own.  `join()` afterwards makes the current stream wait for the second."""
+
+    def __init__(self, side: "torch.cuda.Stream", device):
+        self.side, self.device = side, device
+
+    def __enter__(self):
+        from ..csrc import gemm_tc
+        self.main = torch.cuda.current_stream(self.device)
+        forked = torch.cuda.Event()
+        forked.record(self.main)
+        self.ctx = torch.cuda.stream(self.side)
+        self.ctx.__enter__()
+        self.side.wait_event(forked)
+        self.scratch = gemm_tc.second_scratch()
+        self.scratch.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        self.scratch.__exit__(*exc)
+        self.done = torch.cuda.Event()
+        self.done.record(self.side)
+        self.ctx.__exit__(*exc)
+
+    def join(self):
+        self.main.wait_event(self.done)
