@@ -7,7 +7,7 @@ generation loop, sampling, and hand-written sm_100a kernels under it all.
 
     import qstream_b200 as qs
     model = qs.load_model("folder", dtype="bfloat16")
-    engine = qs.Engine(model, max_batch=8)
+    engine = qs.Engine(model, qs.EngineConfig(max_batch=8))
     out = qs.generate(engine, [[1, 2, 3], [4, 5]], max_new_tokens=16,
                       sampling=qs.SamplingConfig.greedy())
 """
@@ -15,7 +15,7 @@ from .errors import QsError, QStreamError, error_string
 from .config import GptjConfig, config_from_dict, load_config, register_architecture
 from .weights import InitScales, write_model_folder
 from .sampling import SamplingConfig
-from .engine import CausalLM, Engine, GenerationResult, Generator, load_model
+from .engine import CausalLM, Engine, EngineConfig, GenerationResult, Generator, load_model
 
 
 def generate(engine, prompts, max_new_tokens=256, sampling=None, stop_tokens=None, callback=None,
@@ -28,4 +28,4 @@ def generate(engine, prompts, max_new_tokens=256, sampling=None, stop_tokens=Non
 __version__ = "0.1.0"
 __all__ = ["QsError", "QStreamError", "error_string", "GptjConfig", "config_from_dict", "load_config",
            "register_architecture", "InitScales", "write_model_folder", "SamplingConfig", "CausalLM",
-           "Engine", "GenerationResult", "Generator", "load_model", "generate"]
+           "Engine", "EngineConfig", "GenerationResult", "Generator", "load_model", "generate"]

@@ -7,7 +7,11 @@ a page pool of its own: K and V as [entries][pages][kv_heads][page_tokens][head_
 Position p of a slot lies in page `page_table[slot][p // page_tokens]`, row
 `p % page_tokens`.  A group with a window gives back the pages that have fallen out of
 every future query's window.  Pages are handed out before a step runs and given back
-when the sequence ends; nothing is zeroed, because reads are bounded by the length.
+when the sequence ends.  Reads are bounded by the length, with one exception: the
+tensor-core prefill attention multiplies the value rows past a sequence's end, in its
+last page, by weights of exactly zero, and 0 * Inf is NaN.  So a page that held another
+sequence's values is zeroed when it is handed on, unless the step that takes it writes
+all of its rows.
 
 This replaces QStream's single-sequence cache (`QSFKVCache`, include/qsf/engine.h:35-51,
 src/engine.c:296-327; `current_seq_len`), whose int8 storage is not taken over.
@@ -61,11 +65,12 @@ class KvGroup:
         self.pool = PagePool(n_pages)
         self.max_pages = max_pages
         shape = (len(self.entries), n_pages, need.n_kv_heads, page_tokens, need.head_dim)
-        # Zeroed once: the tensor-core prefill kernel multiplies a page's rows beyond the sequence's end by
-        # weights of exactly 0, which must not meet non-finite leftovers.  Pages are not cleared again
-        # when they change hands: what the kernels wrote there is finite.
+        # Zeroed once here; a page that has been used is zeroed again (values only: scores of keys past
+        # the end are replaced, not multiplied) when it is handed on to a step that leaves rows unwritten.
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self._used = np.zeros(n_pages, dtype=bool)
+        self._to_zero: list[int] = []
         self.table_host = np.full((n_slots, max_pages), -1, dtype=np.int32)
         self.table_dev = torch.full((n_slots, max_pages), -1, dtype=torch.int32, device=device)
         self._dirty: set[int] = set()
@@ -87,7 +92,10 @@ class KvGroup:
             return
         row = self.table_host[slot]
         for i in range(have, n):
-            row[i] = self.pool.alloc()
+            page = row[i] = self.pool.alloc()
+            if self._used[page] and new_length < (i + 1) * self.page_tokens:
+                self._to_zero.append(page)          # used before, and this step does not fill it
+            self._used[page] = True
         self.held[slot] += n - have
         self._dirty.add(slot)
 
@@ -119,7 +127,15 @@ class KvGroup:
         self._dirty.add(slot)
 
     def upload(self) -> None:
-        """Bring the device page table up to date (rows that changed)."""
+        """Bring the device page table up to date (rows that changed); clear handed-on pages."""
+        if self._to_zero:
+            if self.v.is_cuda:
+                from ..csrc import ops
+                ids = torch.tensor(self._to_zero, dtype=torch.int32).pin_memory().to(self.v.device, non_blocking=True)
+                ops.zero_pages(self.v, ids)
+            else:
+                self.v[:, self._to_zero] = 0
+            self._to_zero.clear()
         if not self._dirty:
             return
         rows = sorted(self._dirty)

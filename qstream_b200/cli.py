@@ -9,7 +9,9 @@ Options kept with their meaning: -p/--prompt, -n/--max-tokens (256), -t/--temper
 prompt is a list of token ids ("5,17,3"; several requests separated by ';' or given with
 repeated -p, or one per line in --prompt-file), and the chat options are gone.  New:
 --dtype, --max-batch, --max-ctx, --stop-token (repeatable; "none" for no stop token),
---random-weights SEED with --config FILE (writes nothing; weights are made on the device).
+--random-weights SEED with --config FILE (writes nothing; weights are made on the device),
+--check-nan (scan every layer's output for values that are not finite, as the reference's
+`check_nan` switch does, include/qsf/engine.h:31).
 Generated ids go to standard output, one request per line; statistics to standard error as
 in src/main.c:323-332.
 """
@@ -59,6 +61,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--stop-token", action="append", help='stop token id (repeatable); "none" for none; default: eos')
     ap.add_argument("--random-weights", type=int, metavar="SEED", help="random weights instead of a model folder")
     ap.add_argument("--config", help="config.json for --random-weights")
+    ap.add_argument("--narrow-fp32", action="store_true",
+                    help="with --dtype bfloat16: round matrices stored in 32-bit to bfloat16 (default: they stay 32-bit)")
+    ap.add_argument("--check-nan", action="store_true", help="check every layer's output for NaN/Inf (slow)")
     return ap
 
 
@@ -88,7 +93,8 @@ def main(argv=None) -> int:
                 cfg = config_from_dict(json.load(fh))
             model = qs.CausalLM.random(cfg, args.random_weights, args.dtype, "cuda")
         else:
-            model = qs.load_model(args.model, dtype=args.dtype, device="cuda", allow_mmap=not args.no_mmap)
+            model = qs.load_model(args.model, dtype=args.dtype, device="cuda", allow_mmap=not args.no_mmap,
+                                  narrow_fp32_matrices=args.narrow_fp32)
         ctx = args.max_ctx or model.spec.max_positions
         max_batch = max(1, min(args.max_batch, len(prompts)))
         max_tokens = max_batch * (-(-min(ctx, model.spec.max_positions) // 64) * 64)
@@ -96,7 +102,8 @@ def main(argv=None) -> int:
             per_token = sum(2 * n.n_kv_heads * n.head_dim for n in model.kv_needs().values()) * \
                 torch.empty((), dtype=model.runtime.dtype).element_size()
             max_tokens = min(max_tokens, max(64, args.ram_budget * 2**20 // max(per_token, 1) // 64 * 64))
-        engine = qs.Engine(model, max_tokens=max_tokens, max_batch=max_batch, max_context=ctx, verbose=args.verbose)
+        engine = qs.Engine(model, qs.EngineConfig(max_tokens=max_tokens, max_batch=max_batch, max_context=ctx,
+                                                  verbose=args.verbose, check_nan=args.check_nan))
         if args.verbose:
             print(f"[qstream] model loaded in {(time.perf_counter() - t0) * 1e3:.1f} ms "
                   f"({model.n_parameters / 1e6:.1f} M parameters, {args.dtype})", file=sys.stderr)

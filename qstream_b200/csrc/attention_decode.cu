@@ -46,6 +46,10 @@ decode_split_kernel(float* __restrict__ partial, const __nv_bfloat16* __restrict
     const int slot = tok_slot[t];
     if (slot < 0) return;
     const int pos = tok_pos[t];
+    if (pos < 0 || pos >= max_splits * SPLIT) {       // outside what the grid and the scratch cover: report, touch nothing
+        if (threadIdx.x == 0 && split == 0) atomicExch(status, 1);
+        return;
+    }
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
     if (split * SPLIT > pos || (split + 1) * SPLIT <= first) return;       // no visible key in this split
 
@@ -207,6 +211,10 @@ __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, size_t ldo,
         return;
     }
     const int pos = tok_pos[t];
+    if (pos < 0 || pos >= max_splits * SPLIT) {       // the split kernel has reported it; a defined row, no access
+        for (int d = threadIdx.x; d < dh; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+        return;
+    }
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
     const int s_lo = first / SPLIT, s_hi = pos / SPLIT;
     const float* base = partial + ((size_t)t * n_heads + head) * max_splits * (dh + 2);
@@ -241,7 +249,8 @@ QS_API long long qs_attention_decode_scratch(int T_tokens, int n_heads, int dh, 
 // out [T, n_heads * dh] bfloat16.  One query token per row; `max_context` bounds every row's
 // position + 1 and fixes the grid, so the same launch serves every length (CUDA graphs).
 // `scratch`: float32, at least qs_attention_decode_scratch(...) elements; contents need no
-// initialisation.
+// initialisation.  A row whose position is negative or not below max_context rounded up to 256 sets
+// status 1 and gets zeros; `tok_slot` entries must be negative (padding) or rows of `page_table`.
 QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long long ldq, const void* k_cache,
                                const void* v_cache, const int32_t* page_table, int max_pages, int page_tokens,
                                const int32_t* tok_slot, const int32_t* tok_pos, int T_tokens, int n_heads,
@@ -266,11 +275,13 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
     const int nch = (n_chunks + (1 << gs_log2) - 1) >> gs_log2;
     dim3 grid(max_splits, n_heads, T_tokens);
     const size_t smem = (size_t)WARPS * dh * sizeof(float);
-    static int sm_count = 0;
+    static int sm_counts[64] = {0};                  // per device; a race only repeats the query
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    int sm_count = sm_counts[dev];
     if (sm_count == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            sm_count = 1;
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sm_count = 1;
+        sm_counts[dev] = sm_count;
     }
     const bool few_ctas = (long long)max_splits * n_heads * T_tokens <= 2LL * sm_count;
 #define GO(NCH, UNROLL) decode_split_kernel<NCH, UNROLL><<<grid, WARPS * 32, smem, stream>>>( \
@@ -297,9 +308,12 @@ QS_API int qs_attention_decode(void* out, long long ldo, const void* q, long lon
 // In host code this name is only a handle for cudaGetSymbolAddress, not a device address.
 static __device__ __align__(256) float g_decode_static_scratch[QS_DECODE_STATIC_SCRATCH_FLOATS];
 
+#include <mutex>
+
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_decode_static_ptr[kMaxDevices] = {nullptr};
+std::mutex g_decode_static_mutex;                  // set-up from two host threads at once
 }  // namespace
 
 QS_API int qs_attention_decode_static(void* out, long long ldo, const void* q, long long ldq,
@@ -318,14 +332,19 @@ QS_API int qs_attention_decode_static(void* out, long long ldo, const void* q, l
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
     QS_REQUIRE(device >= 0 && device < kMaxDevices, "attention_decode_static: device %d out of range", device);
-    if (!g_decode_static_ptr[device]) {             // first call on this device: find the array's device address
-        float* p = nullptr;
-        e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
-        if (e != cudaSuccess || !p)
-            return qs_fail(QS_ERR_INTERNAL, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-        g_decode_static_ptr[device] = p;
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_decode_static_mutex);
+        if (!g_decode_static_ptr[device]) {         // first call on this device: find the array's device address
+            float* p = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
+            if (e != cudaSuccess || !p)
+                return qs_fail(QS_ERR_INTERNAL, "attention_decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_decode_static_ptr[device] = p;
+        }
+        scratch = g_decode_static_ptr[device];
     }
     return qs_attention_decode(out, ldo, q, ldq, k_cache, v_cache, page_table, max_pages, page_tokens, tok_slot,
                                tok_pos, T_tokens, n_heads, n_kv_heads, dh, scale, window, max_context,
-                               g_decode_static_ptr[device], status, stream);
+                               scratch, status, stream);
 }

@@ -8,7 +8,7 @@ loaded, or a tensor is not on a CUDA device, the call raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_longlong, c_void_p
+from ctypes import c_double, c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
 
 import torch
 
@@ -39,6 +39,13 @@ _SIGNATURES = {
     "qs_argmax": ([c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p], c_int),
     "qs_repeat_penalty": ([c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_void_p, c_float, c_void_p], c_int),
     "qs_sample": ([c_void_p, c_void_p, c_int, c_int, c_longlong, c_float, c_int, c_float, c_void_p, c_void_p], c_int),
+    "qs_random_fill": ([c_void_p, c_int, c_longlong, c_ulonglong, c_int, c_double, c_longlong, c_void_p], c_int),
+    "qs_convert": ([c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p], c_int),
+    "qs_check_finite": ([c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p], c_int),
+    "qs_canary_fill": ([c_void_p, c_longlong, c_uint, c_void_p], c_int),
+    "qs_canary_check": ([c_void_p, c_longlong, c_uint, c_void_p, c_void_p], c_int),
+    "qs_take_tokens": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p], c_int),
+    "qs_zero_pages": ([c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p], c_int),
 }
 
 
@@ -212,7 +219,7 @@ def linear_simt(x, weight, bias=None, activation=None, residuals=(), out_dtype=N
 def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_slot, tok_pos,
                page_table, page_tokens, k_cache, v_cache, status) -> None:
     """Rotate q (in place) and k, and write k and v into the paged cache entry.
-    k = v = None (n_kv_heads = 0): rotate q only."""
+    k = v = None (n_kv_heads = 0): rotate q only (no page table is needed then)."""
     ref = k if k is not None else q
     T = ref.shape[0]
     max_pos = cos_sin.shape[0] if cos_sin is not None else 0
@@ -221,7 +228,8 @@ def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_
         k.stride(0) if k is not None else 0, v.stride(0) if v is not None else 0,
         n_heads if q is not None else 0, n_kv_heads, head_dim, rotary_dim if cos_sin is not None else 0,
         ptr(cos_sin), max_pos, _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
-        _int32(page_table, "page_table"), page_table.shape[1], page_tokens, ptr(k_cache), ptr(v_cache), T,
+        _int32(page_table, "page_table") if page_table is not None else None,
+        page_table.shape[1] if page_table is not None else 0, page_tokens, ptr(k_cache), ptr(v_cache), T,
         ptr(status), stream()))
 
 
@@ -264,3 +272,63 @@ def sample(logits, temperature: float, top_k: int, top_p: float, draws, out=None
     check(library().qs_sample(ptr(out), ptr(logits), rows, V, ld, float(temperature), int(top_k),
                               float(top_p), ptr(draws), stream()))
     return out
+
+
+# ------------------------------------------------------------------------------- utility kernels
+
+_FILL_TYPES = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 2}
+_CONVERT_IN = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def random_fill(out: torch.Tensor, key: int, kind: int, a: float, first: int = 0) -> torch.Tensor:
+    """Fill `out` (contiguous; float32, bfloat16 or int32) with elements first.. of the stream `key`:
+    kind 0 N(0, a), kind 1 1 + U(-a, a), kind 2 integers below a."""
+    if not out.is_contiguous() or out.dtype not in _FILL_TYPES:
+        raise QStreamError(QsError.INVALID_INPUT, "random fill: need a contiguous float32, bfloat16 or int32 tensor")
+    check(library().qs_random_fill(ptr(out), _FILL_TYPES[out.dtype], out.numel(), int(key) & (2**64 - 1), int(kind),
+                                   float(a), int(first), stream()))
+    return out
+
+
+def convert(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """A copy of `src` (float32, bfloat16 or float16, contiguous) in float32 or bfloat16, rounded to
+    nearest even."""
+    if not src.is_contiguous() or src.dtype not in _CONVERT_IN or dtype not in (torch.float32, torch.bfloat16):
+        raise QStreamError(QsError.INVALID_INPUT, f"convert: {src.dtype} -> {dtype} is not offered")
+    out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    check(library().qs_convert(ptr(out), _FILL_TYPES[dtype], ptr(src), _CONVERT_IN[src.dtype], src.numel(), stream()))
+    return out
+
+
+def check_finite(x: torch.Tensor, tag: int, record: torch.Tensor, row_slot=None) -> None:
+    """Scan x [rows, width]; the first value that is not finite sets record = (1, tag, row, column).
+    Rows with a negative `row_slot` entry are skipped."""
+    rows, width, ld = _rows(x)
+    check(library().qs_check_finite(ptr(x), dtype_code(x), rows, width, ld, int(tag),
+                                    _int32(row_slot, "row_slot") if row_slot is not None else None,
+                                    _int32(record, "record"), stream()))
+
+
+def canary_fill(words: torch.Tensor, pattern: int) -> None:
+    check(library().qs_canary_fill(ptr(words), words.numel() * words.element_size() // 4, pattern & 0xFFFFFFFF, stream()))
+
+
+def canary_check(words: torch.Tensor, pattern: int, damaged: torch.Tensor) -> None:
+    """Adds the number of damaged guard words to damaged[0] (int32 [2] on the device)."""
+    check(library().qs_canary_check(ptr(words), words.numel() * words.element_size() // 4, pattern & 0xFFFFFFFF,
+                                    _int32(damaged, "damaged"), stream()))
+
+
+def take_tokens(dst: torch.Tensor, src: torch.Tensor, idx: torch.Tensor, n: int) -> None:
+    """dst[j] = src[idx[j]] for j < n where idx[j] >= 0 (all int32, on the device)."""
+    check(library().qs_take_tokens(_int32(dst, "dst"), _int32(src, "src"), _int32(idx, "idx"), int(n),
+                                   src.numel(), stream()))
+
+
+def zero_pages(storage: torch.Tensor, pages: torch.Tensor) -> None:
+    """Zero the listed pages (int32, device) of every entry of a cache tensor [entries, pages, ...]."""
+    if not storage.is_contiguous():
+        raise QStreamError(QsError.INVALID_INPUT, "zero pages: the cache tensor must be contiguous")
+    page_bytes = storage.stride(1) * storage.element_size()
+    check(library().qs_zero_pages(ptr(storage), storage.stride(0) * storage.element_size(), page_bytes,
+                                  storage.shape[0], _int32(pages, "pages"), pages.numel(), storage.shape[1], stream()))

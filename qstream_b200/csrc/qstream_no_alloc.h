@@ -28,6 +28,10 @@
  *    overlap on the GPU (different streams, no ordering between them) race on the array and
  *    give wrong results; calls on one stream, or ordered by events, are safe.
  *
+ *  - Bounds the caller keeps: every `tok_pos[t]` lies in [0, max_context rounded up to 256) -
+ *    a position outside sets the status word to 1 and gives that row zeros, nothing is read
+ *    for it; every `tok_slot[t]` is negative (a padding row: zeros) or a row of `page_table`.
+ *
  * Arguments are those of `qs_attention_decode` without `scratch`.
  */
 #ifndef QSTREAM_NO_ALLOC_H

@@ -103,32 +103,53 @@ class Generator:
 
     def _run_batch(self, batch, prompts, max_new_tokens, sampler, sampling, stop, callback,
                    emit_stop_token, result) -> None:
+        """One batch from its prompts to its last token.
+
+        The decisions (who stops, and why) are taken in one place, after the host has read the step's
+        tokens.  What differs between engines is only *when* the next step is launched.  An engine
+        that takes tokens from the device (`accepts_device_tokens` with graphs) is run ahead: the
+        sampled tokens feed the next step on the device, and that step is launched before the host has
+        read them, for every sequence that could go on whatever its token is (not at its token limit,
+        room in the context); the host reads the tokens (a copy into pinned memory) while the step runs.
+        A sequence that turns out to have stopped has then been stepped once too often, which only costs
+        the work: its slot is given back all the same and nothing it wrote is read.  Any other engine is
+        stepped after the decisions, with the tokens from the host."""
         eng = self.engine
-        if getattr(eng, "accepts_device_tokens", False) and getattr(eng, "use_graphs", False):
-            return self._run_batch_pipelined(batch, prompts, max_new_tokens, sampler, sampling, stop, callback,
-                                             emit_stop_token, result)
+        run_ahead = bool(getattr(eng, "accepts_device_tokens", False) and getattr(eng, "use_graphs", False))
         max_context = eng.cache.max_context
         slots = {i: eng.acquire() for i in batch}
         states = {i: RequestSamplingState(sampling, i, prompts[i]) for i in batch}
         live = list(batch)
+        reader = _TokenReader(len(batch))
         try:
             t0 = time.perf_counter()
             logits = eng.step([slots[i] for i in live], [list(prompts[i]) for i in live])
             first = True
             while live:
-                chosen = sampler.sample(logits, [states[i] for i in live])
-                chosen = [int(t) for t in (chosen.tolist() if hasattr(chosen, "tolist") else chosen)]
+                chosen_dev = sampler.sample(logits, [states[i] for i in live])
+                n = len(live)
+                reader.start(chosen_dev, n)
+                ahead, may = None, []
+                if run_ahead and not self.interrupted:
+                    # who goes on whatever the token is: not at the token limit, room in the context
+                    may = [k for k, i in enumerate(live)
+                           if len(result.tokens[i]) + 1 < max_new_tokens
+                           and len(prompts[i]) + len(result.tokens[i]) + 1 <= max_context]
+                    if may:
+                        from .step import TokenFeed
+                        ahead = eng.step([slots[live[k]] for k in may], TokenFeed(chosen_dev, may))
+                chosen = reader.finish()
                 now = time.perf_counter()
                 if first:
                     result.prefill_tokens += sum(len(prompts[i]) for i in live)
                     result.prefill_seconds += now - t0
                     first = False
                 else:
-                    result.decode_tokens += len(live)
+                    result.decode_tokens += n
                     result.decode_seconds += now - t0
                 t0 = now
-                go_on, feed = [], []
-                for i, tok in zip(live, chosen):
+                go_on, go_on_at, feed = [], [], []
+                for k, (i, tok) in enumerate(zip(live, chosen)):
                     out = result.tokens[i]
                     reason = None
                     if tok in stop:
@@ -148,98 +169,55 @@ class Generator:
                             reason = "interrupted"
                     if reason is None:
                         go_on.append(i)
+                        go_on_at.append(k)
                         feed.append([tok])
                     else:
                         result.finish_reasons[i] = reason
                         eng.release(slots.pop(i))
                 live = go_on
-                if live:
+                if not live:
+                    break
+                if ahead is not None and all(k in may for k in go_on_at):
+                    rows = [may.index(k) for k in go_on_at]
+                    logits = ahead if len(rows) == len(may) else eng.rows_of(ahead, rows)
+                else:                               # nothing was run ahead (or not for all of them): step now
                     logits = eng.step([slots[i] for i in live], feed)
+            check = getattr(eng, "check_status", None)
+            if check is not None:
+                check()                             # a kernel's fault report ends the batch with an error, not with tokens
         finally:
             for i in list(slots):
                 eng.release(slots.pop(i))
                 if result.finish_reasons[i] is None:
                     result.finish_reasons[i] = "interrupted"
 
-    def _run_batch_pipelined(self, batch, prompts, max_new_tokens, sampler, sampling, stop, callback,
-                             emit_stop_token, result) -> None:
-        """The same decisions with the device kept busy: the sampled tokens go from the sampler to the
-        next step on the device, and that step is launched before the host has read them.  The host
-        reads them (a copy into pinned memory) while the step runs and then decides who goes on; a
-        sequence that turns out to have stopped has been stepped once too often, which only costs the
-        work: its slot is given back all the same."""
-        import torch
-        from ..csrc import ops
-        eng = self.engine
-        max_context = eng.cache.max_context
-        slots = {i: eng.acquire() for i in batch}
-        states = {i: RequestSamplingState(sampling, i, prompts[i]) for i in batch}
-        live = list(batch)
-        host = torch.empty(len(batch), dtype=torch.int32).pin_memory()
-        try:
-            t0 = time.perf_counter()
-            logits = eng.step([slots[i] for i in live], [list(prompts[i]) for i in live])
-            first = True
-            while live:
-                chosen_dev = sampler.sample(logits, [states[i] for i in live])
-                n = len(live)
-                host[:n].copy_(chosen_dev, non_blocking=True)
-                copied = torch.cuda.Event()
-                copied.record()
-                # who may go on whatever the token is: not at the token limit, room in the context
-                may = [k for k, i in enumerate(live)
-                       if len(result.tokens[i]) + 1 < max_new_tokens
-                       and len(prompts[i]) + len(result.tokens[i]) + 1 <= max_context and not self.interrupted]
-                next_logits = None
-                if may:
-                    feed = chosen_dev if len(may) == n else chosen_dev[torch.tensor(may, device=chosen_dev.device)].contiguous()
-                    next_logits = eng.step([slots[live[k]] for k in may], feed)
-                copied.synchronize()
-                chosen = host[:n].tolist()
-                now = time.perf_counter()
-                if first:
-                    result.prefill_tokens += sum(len(prompts[i]) for i in live)
-                    result.prefill_seconds += now - t0
-                    first = False
-                else:
-                    result.decode_tokens += n
-                    result.decode_seconds += now - t0
-                t0 = now
-                may_set = set(may)
-                go_on_rows, go_on = [], []
-                for k, (i, tok) in enumerate(zip(live, chosen)):
-                    out = result.tokens[i]
-                    reason = None
-                    if tok in stop:
-                        reason = "stop"
-                        if emit_stop_token:
-                            out.append(tok)
-                    else:
-                        out.append(tok)
-                        states[i].push(tok)
-                        if callback is not None and callback(i, tok):
-                            reason = "callback"
-                        elif len(out) >= max_new_tokens:
-                            reason = "length"
-                        elif len(prompts[i]) + len(out) > max_context:
-                            reason = "context"
-                        elif self.interrupted or k not in may_set:
-                            reason = "interrupted"
-                    if reason is None:
-                        go_on.append(i)
-                        go_on_rows.append(may.index(k))
-                    else:
-                        result.finish_reasons[i] = reason
-                        eng.release(slots.pop(i))
-                live = go_on
-                if live:
-                    if len(go_on_rows) == len(may):
-                        logits = next_logits
-                    else:
-                        rows = torch.tensor(go_on_rows, dtype=torch.int32).pin_memory().to(next_logits.device, non_blocking=True)
-                        logits = ops.gather_rows(next_logits, rows)
-        finally:
-            for i in list(slots):
-                eng.release(slots.pop(i))
-                if result.finish_reasons[i] is None:
-                    result.finish_reasons[i] = "interrupted"
+
+class _TokenReader:
+    """Brings a step's sampled tokens to the host.  Tokens on a CUDA device are copied into pinned
+    memory without waiting (`start`) and awaited later (`finish`), so that work launched in between
+    overlaps the copy; anything else (a list, a host tensor) is read at once."""
+
+    def __init__(self, n_max: int):
+        self.n_max = n_max
+        self.host = None
+        self.event = None
+        self.now = None
+
+    def start(self, chosen, n: int) -> None:
+        if getattr(chosen, "is_cuda", False):
+            import torch
+            if self.host is None:
+                self.host = torch.empty(self.n_max, dtype=torch.int32).pin_memory()
+            self.host[:n].copy_(chosen, non_blocking=True)
+            self.event = torch.cuda.Event()
+            self.event.record()
+            self.now = n
+        else:
+            self.event = None
+            self.now = [int(t) for t in (chosen.tolist() if hasattr(chosen, "tolist") else chosen)]
+
+    def finish(self) -> list:
+        if self.event is None:
+            return self.now
+        self.event.synchronize()
+        return self.host[:self.now].tolist()

@@ -15,7 +15,7 @@ import weakref
 import numpy as np
 import torch
 
-from .step import StepBatch, StepContext
+from .step import StepBatch, StepContext, TokenFeed
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 _RING = 4
@@ -35,7 +35,7 @@ class DecodeGraph:
         self._engine = weakref.ref(engine)          # the engine owns its graphs, not the other way round
         self.rows = rows
         dev = engine.device
-        sizes = [rows, rows, rows, rows, rows, rows + 1, rows]
+        sizes = [rows, rows, rows, rows, rows, rows + 1, rows, rows]        # the last: where a fed token comes from
         self.offs = np.concatenate([[0], np.cumsum(sizes)]).astype(int)
         n = int(self.offs[-1])
         self.meta = torch.zeros(n, dtype=torch.int32, device=dev)
@@ -43,12 +43,14 @@ class DecodeGraph:
         self.staging_np = [s.numpy() for s in self.staging]
         self.events = [None] * _RING
         self.turn = 0
-        v = [self.meta[self.offs[i]:self.offs[i + 1]] for i in range(7)]
+        v = [self.meta[self.offs[i]:self.offs[i + 1]] for i in range(8)]
+        self.tok_src = v[7]
         # fixed parts of the metadata: every row is wanted, row i is sequence i
         for s in self.staging_np:
             s[self.offs[1]:self.offs[2]] = -1
             s[self.offs[3]:self.offs[4]] = np.arange(rows)
             s[self.offs[5]:self.offs[6]] = np.arange(rows + 1)
+            s[self.offs[7]:self.offs[8]] = -1
         self.meta.copy_(self.staging[0])
         self.batch = StepBatch(n_seq=rows, n_tokens=rows, n_want=rows, tokens=v[0], tok_slot=v[1], tok_pos=v[2],
                                want_rows=v[3], seq_slot=v[4], seq_start=v[5], seq_p0=v[6],
@@ -60,7 +62,7 @@ class DecodeGraph:
     def capture(self) -> None:
         from ..csrc import ops
         eng = self._engine()
-        ctx = StepContext(self.batch, eng.cache, eng.status, eng.side_stream)
+        ctx = StepContext(self.batch, eng.cache, eng.status, eng.side_stream, eng.nan_record)
         stream = torch.cuda.Stream(device=eng.device)
         stream.wait_stream(torch.cuda.current_stream(eng.device))
         with torch.cuda.stream(stream):
@@ -85,7 +87,7 @@ class DecodeGraph:
 
     def run(self, slots, tokens, p0) -> torch.Tensor:
         """Refresh the metadata and replay; returns the logits buffer [rows, vocab].
-        `tokens`: a list of ints, or an int32 device tensor [len(slots)] (no host round trip)."""
+        `tokens`: a list of ints, or a `TokenFeed` (the tokens are on the device: no host round trip)."""
         if self.graph is None:
             self.capture()          # while the metadata still holds padding only: the warm-up run touches no sequence
         i = self.turn
@@ -93,8 +95,10 @@ class DecodeGraph:
         if self.events[i] is not None:
             self.events[i].synchronize()                # the copy that last read this buffer is done
         s, o, n = self.staging_np[i], self.offs, len(slots)
-        on_device = isinstance(tokens, torch.Tensor)
+        on_device = isinstance(tokens, TokenFeed)
         s[o[0]:o[0] + n] = 0 if on_device else tokens
+        s[o[7]:o[7] + n] = tokens.rows if on_device else -1
+        s[o[7] + n:o[8]] = -1
         s[o[0] + n:o[1]] = 0
         s[o[1]:o[1] + n] = slots
         s[o[1] + n:o[2]] = -1
@@ -105,12 +109,12 @@ class DecodeGraph:
         s[o[6]:o[6] + n] = p0
         s[o[6] + n:o[7]] = 0
         self.meta.copy_(self.staging[i], non_blocking=True)
+        from ..csrc import ops
         if on_device:                                   # the sampler's output goes straight into the graph's input
-            self.meta[o[0]:o[0] + n].copy_(tokens, non_blocking=True)
+            ops.take_tokens(self.batch.tokens, tokens.buffer, self.tok_src, n)
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
         self.graph.replay()
-        from ..csrc import ops
         ops.count_launches(self.launches)
         return self.logits

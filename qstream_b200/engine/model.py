@@ -90,14 +90,18 @@ class CausalLM:
 
     # ------------------------------------------------------------------ making a model
     @classmethod
-    def from_folder(cls, folder, dtype="bfloat16", device="cuda", allow_mmap=True, verbose=0):
-        """config.json chooses the architecture; *.safetensors give the weights."""
+    def from_folder(cls, folder, dtype="bfloat16", device="cuda", allow_mmap=True, verbose=0,
+                    narrow_fp32_matrices=False):
+        """config.json chooses the architecture; *.safetensors give the weights.
+        narrow_fp32_matrices: round matrices that the files store in 32-bit to bfloat16 in a
+        bfloat16 engine (default: a tensor stored in 32-bit stays in 32-bit)."""
         config = load_config(folder)
         spec = config.model_spec()
         files = open_checkpoint(folder, allow_mmap)
         try:
             tensors = bind_tensors(files, declared_tensors(spec), resolve_dtype(dtype), device,
-                                   getattr(config, "ignored_tensor_suffixes", ()))
+                                   getattr(config, "ignored_tensor_suffixes", ()),
+                                   narrow_fp32_matrices=narrow_fp32_matrices)
         finally:
             for f in files:
                 f.close()
@@ -150,14 +154,25 @@ class CausalLM:
         """Run the step's tokens through every scheduled layer; return float32 logits
         [n_want, vocab] of the wanted rows (None if none is wanted)."""
         b = step.batch
+        record = getattr(step, "nan_record", None)      # the finite check (QStream's check_nan, src/engine.c:1176-1187)
+        n_runs = len(self.spec.schedule)
         x = ops.embedding(self.wte, b.tokens, self.runtime.dtype)
-        for run in self.spec.schedule:
+        if record is not None:
+            ops.check_finite(x, n_runs, record, b.tok_slot)
+        for i, run in enumerate(self.spec.schedule):
             x = self.blocks[run.layer].forward(x, step, run.cache)
+            if record is not None:
+                ops.check_finite(x, i, record, b.tok_slot)
         if b.n_want == 0:
             return None
         rows = ops.gather_rows(x, b.want_rows)
         z = self.final_norm.forward(rows)
-        return linear(z, self.head_weight, self.head_bias, out_dtype=torch.float32)
+        logits = linear(z, self.head_weight, self.head_bias, out_dtype=torch.float32)
+        if record is not None:
+            # a captured decode step wants every row, padding included: row i of the logits is row i of the step
+            every_row = b.decode and b.n_want == b.n_tokens
+            ops.check_finite(logits, n_runs + 1, record, b.tok_slot if every_row else None)
+        return logits
 
 
 def load_model(folder, dtype="bfloat16", device="cuda", **kw) -> CausalLM:

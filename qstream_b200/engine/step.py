@@ -14,7 +14,7 @@ every kernel that touches the cache.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass, field, replace
 from typing import Optional, Sequence
 
 import numpy as np
@@ -46,15 +46,51 @@ class StepBatch:
     max_total: int = 0              # longest sequence after this step
 
 
+@dataclass
+class TokenFeed:
+    """Tokens that are still on the device: sequence j of the step takes `buffer[rows[j]]`.
+    `buffer` is the sampler's int32 output; the host need not have read it."""
+    buffer: object
+    rows: Sequence[int]
+
+
+@dataclass
+class EngineConfig:
+    """How an engine is set up, in the manner of QStream's `QSFEngineConfig` with its
+    `qsf_engine_config_default` (include/qsf/engine.h:25-32, src/engine.c:19-26).
+
+    max_batch: the most sequences alive at once.  max_context: the longest sequence (0: the
+    model's positions).  max_tokens: the tokens all live sequences may hold together, each
+    rounded up to a whole page of 64; it sizes the cache (0: max_batch * max_context).
+    mem_budget: bytes of device memory the cache may take (0: what is free).  check_nan: scan
+    every layer's output for values that are not finite and raise NAN_DETECTED with the layer
+    and the place (the reference's switch, src/engine.c:1176-1187); it makes every step wait
+    for the device.  use_graphs: replay decode steps as CUDA graphs."""
+    max_batch: int = 64
+    max_context: int = 0
+    max_tokens: int = 0
+    mem_budget: int = 0
+    verbose: int = 0
+    check_nan: bool = False
+    use_graphs: bool = True
+
+    @classmethod
+    def default(cls) -> "EngineConfig":
+        return cls()
+
+
 class StepContext:
     """What a part may touch during a step."""
 
-    def __init__(self, batch: StepBatch, cache: SequenceCache, status: torch.Tensor, side_stream=None):
+    def __init__(self, batch: StepBatch, cache: SequenceCache, status: torch.Tensor, side_stream=None,
+                 nan_record: Optional[torch.Tensor] = None):
         self.batch = batch
         self.cache = cache
         self.status = status
         # a second CUDA stream for work that does not depend on the mixer (None: everything in order)
         self.side_stream = side_stream
+        # int32 [4] on the device when every layer's output is to be scanned for values that are not finite
+        self.nan_record = nan_record
 
     def kv(self, cache_id: int):
         return self.cache.view(cache_id)
@@ -74,41 +110,53 @@ STATUS_MESSAGES = {
 class Engine:
     """A model with its cache: sequences are acquired, stepped and released.
 
-    max_tokens: the tokens all live sequences may hold together, each rounded up to a
-    whole page of 64; it sizes the cache.  max_batch: the most sequences alive at once.
-    max_context: the longest sequence (default: the model's positions).
+    Set up from an `EngineConfig` (default: `EngineConfig.default()`); keyword arguments
+    with the names of its fields override single fields.
     """
 
-    def __init__(self, model: CausalLM, max_tokens: Optional[int] = None, max_batch: int = 64,
-                 max_context: Optional[int] = None, verbose: int = 0, use_graphs: bool = True):
+    def __init__(self, model: CausalLM, config: Optional[EngineConfig] = None, **overrides):
+        cfg = config or EngineConfig.default()
+        unknown = [k for k in overrides if not hasattr(cfg, k)]
+        if unknown:
+            raise QStreamError(QsError.INVALID_INPUT, f"Engine: unknown option(s) {unknown}")
+        cfg = replace(cfg, **{k: (v if v is not None else getattr(EngineConfig, k)) for k, v in overrides.items()})
+        self.config = cfg
         self.model = model
         self.device = model.runtime.device
         self.dtype = model.runtime.dtype
-        self.verbose = verbose
-        ctx = model.spec.max_positions if not max_context else min(max_context, model.spec.max_positions)
-        if max_tokens is None:
-            max_tokens = max_batch * ctx
+        self.verbose = verbose = cfg.verbose
+        ctx = model.spec.max_positions if not cfg.max_context else min(cfg.max_context, model.spec.max_positions)
+        max_batch = cfg.max_batch
+        max_tokens = cfg.max_tokens or max_batch * ctx
         self.max_batch = max_batch
         kv_needs, state_needs = model.kv_needs(), model.state_needs()
-        self._check_budget(kv_needs, max_tokens)
+        self._check_budget(kv_needs, max_tokens, cfg.mem_budget)
         self.cache = SequenceCache(kv_needs, state_needs, max_tokens, max_batch, ctx, self.dtype, self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # words the kernels report through: [0] a fault code, [4:8] the finite check's record
+        self._words = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.status = self._words[0:1]
+        self.check_nan = cfg.check_nan
+        self.nan_record = self._words[4:8] if cfg.check_nan else None
         # decode steps run the feed-forward's first product beside the attention kernels
         self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
-        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self.use_graphs = cfg.use_graphs and self.device.type == "cuda"
         self._graphs = {}
-        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else None
+        self._words_host = torch.zeros(9, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else None
         if verbose:
             import sys
             print(f"[qstream] cache: {self.cache.bytes / 2**20:.1f} MB for {max_tokens} tokens, "
                   f"{self.cache.slots.n_slots} slots, context {ctx}; weights {model.weight_bytes / 2**20:.1f} MB",
                   file=sys.stderr)
 
-    def _check_budget(self, kv_needs, max_tokens):
-        if self.device.type != "cuda":
-            return
+    def _check_budget(self, kv_needs, max_tokens, mem_budget=0):
         elem = torch.empty((), dtype=self.dtype).element_size()
         want = sum(2 * max_tokens * n.n_kv_heads * n.head_dim * elem for n in kv_needs.values())
+        if mem_budget and want > mem_budget:
+            raise QStreamError(QsError.BUDGET_EXCEEDED,
+                               f"a cache of {max_tokens} tokens needs {want / 2**20:.1f} MiB, "
+                               f"the budget is {mem_budget / 2**20:.1f} MiB")
+        if self.device.type != "cuda":
+            return
         free, _ = torch.cuda.mem_get_info(self.device)
         if want > free:
             raise QStreamError(QsError.BUDGET_EXCEEDED,
@@ -185,25 +233,35 @@ class Engine:
             return t.pin_memory().to(self.device, non_blocking=True)
         return t
 
-    accepts_device_tokens = True        # step() also takes an int32 device tensor with one token per sequence
+    accepts_device_tokens = True        # step() also takes a `TokenFeed`: one token per sequence, still on the device
 
-    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
-             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
-        """Run one step.  `want[i]` lists the places among sequence i's new tokens whose
-        logits are asked for (default: the last).  Returns float32 logits [n_want, vocab]
-        on the device, in the order of the sequences and of `want`; None if none is wanted."""
-        if isinstance(tokens, torch.Tensor):
+    def step(self, slots: Sequence[int], tokens, want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """Run one step.  `tokens[i]` are sequence i's next tokens (any number, none for a
+        sequence that idles in this step); a `TokenFeed` gives one token per sequence from a
+        device buffer instead.  `want[i]` lists the places among sequence i's new tokens whose
+        logits are asked for (default: the last).  Returns float32 logits [n_want, vocab] on
+        the device, in the order of the sequences and of `want`; None if none is wanted.
+
+        The logits of a decode step (one token per sequence) are a view of a buffer that the
+        next decode step of the same batch size overwrites: copy what must outlive it."""
+        if isinstance(tokens, TokenFeed):
             if not self.use_graphs:
-                tokens = [[int(t)] for t in tokens.tolist()]
+                host = tokens.buffer.tolist()
+                tokens = [[int(host[r])] for r in tokens.rows]
             else:
-                return self._decode_step(slots, tokens, want)
-        if self.use_graphs and tokens and all(len(t) == 1 for t in tokens):
-            return self._decode_step(slots, tokens, want)
+                return self._finish(self._decode_step(slots, tokens, want))
+        if self.use_graphs and len(tokens) > 0 and all(len(t) == 1 for t in tokens):
+            return self._finish(self._decode_step(slots, tokens, want))
         batch = self.build_batch(slots, tokens, want)
         if batch.n_tokens == 0:
             return None
-        logits = self.model.forward(StepContext(batch, self.cache, self.status, self.side_stream))
+        logits = self.model.forward(StepContext(batch, self.cache, self.status, self.side_stream, self.nan_record))
         self.cache.commit(batch.slots, batch.new_tokens)
+        return self._finish(logits)
+
+    def _finish(self, logits):
+        if self.check_nan:
+            self.check_status()
         return logits
 
     def _decode_step(self, slots, tokens, want):
@@ -211,12 +269,16 @@ class Engine:
         from ..csrc import ops
         from .graphs import DecodeGraph, bucket_for
         n = len(slots)
-        if (not isinstance(tokens, torch.Tensor) and len(tokens) != n) or (want is not None and len(want) != n):
+        fed = isinstance(tokens, TokenFeed)
+        if (len(tokens.rows) if fed else len(tokens)) != n or (want is not None and len(want) != n):
             raise QStreamError(QsError.INVALID_INPUT, "step: slots, tokens and want differ in length")
         V = self.model.vocab_size
-        if isinstance(tokens, torch.Tensor):            # one token per sequence, already on the device (from the sampler)
-            if tokens.dtype != torch.int32 or tokens.numel() != n or not tokens.is_cuda or not tokens.is_contiguous():
-                raise QStreamError(QsError.INVALID_INPUT, "step: device tokens must be a contiguous int32 tensor, one per sequence")
+        if fed:
+            buf = tokens.buffer
+            if buf.dtype != torch.int32 or not buf.is_cuda or not buf.is_contiguous() or buf.dim() != 1:
+                raise QStreamError(QsError.INVALID_INPUT, "step: fed tokens must be a contiguous int32 device vector")
+            if any(not 0 <= int(r) < buf.numel() for r in tokens.rows):
+                raise QStreamError(QsError.INVALID_INPUT, "step: a fed token's row lies outside the buffer")
             toks = tokens
         else:
             toks = [int(t[0]) for t in tokens]
@@ -241,16 +303,42 @@ class Engine:
         picked = [i for i, w in enumerate(want) for _ in w]
         if not picked:
             return None
-        idx = torch.tensor(picked, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        return self.rows_of(logits, picked)
+
+    def rows_of(self, logits: torch.Tensor, rows: Sequence[int]) -> torch.Tensor:
+        """The listed rows of a logits tensor, as a new tensor."""
+        from ..csrc import ops
+        idx = torch.tensor(list(rows), dtype=torch.int32)
+        idx = idx.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else idx
         return ops.gather_rows(logits, idx)
 
     def check_status(self) -> None:
-        """Raise if a kernel reported a fault (this waits for the device)."""
-        if self._status_host is None:
-            code = int(self.status.item())
+        """Raise if a kernel reported a fault, a bounded wait ran out, or (with `check_nan`) a
+        layer's output held a value that is not finite.  This waits for the device."""
+        if self._words_host is None:
+            words = self._words.tolist() + [0]
         else:
-            self._status_host.copy_(self.status, non_blocking=False)
-            code = int(self._status_host.item())
-        if code:
-            self.status.zero_()
-            raise QStreamError(QsError.INTERNAL, STATUS_MESSAGES.get(code, f"kernel status {code}"))
+            from ..csrc import gemm_tc
+            self._words_host[:8].copy_(self._words, non_blocking=True)
+            self._words_host[8:9].copy_(gemm_tc.status_word(self.device), non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            words = self._words_host.tolist()
+        code, nan, gemm = words[0], words[4:8], words[8]
+        if not (code or nan[0] or gemm):
+            return
+        self._words.zero_()
+        if gemm:
+            from ..csrc import gemm_tc
+            gemm_tc.status_word(self.device).zero_()
+        if nan[0]:
+            n_runs = len(self.model.spec.schedule)
+            where = f"schedule entry {nan[1]}" if nan[1] < n_runs else ("the logits" if nan[1] == n_runs + 1 else "the embedding")
+            raise QStreamError(QsError.NAN_DETECTED,
+                               f"a value that is not finite in the output of {where} (layer "
+                               f"{self.model.spec.schedule[nan[1]].layer if nan[1] < n_runs else '-'}), "
+                               f"row {nan[2]} of the step, element {nan[3]}")
+        if gemm:
+            raise QStreamError(QsError.INTERNAL, f"tensor-core matrix product: a wait inside the kernel ran out (code {gemm})")
+        if code >= 100:
+            raise QStreamError(QsError.INTERNAL, f"attention: a wait inside the kernel ran out (code {code})")
+        raise QStreamError(QsError.INTERNAL, STATUS_MESSAGES.get(code, f"kernel status {code}"))

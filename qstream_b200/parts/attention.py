@@ -95,7 +95,7 @@ class Attention(Mixer):
             if self.position is not None and table is None:
                 self.position.apply(q, k, step, s.n_heads, s.n_kv_heads, s.head_dim)
             ops.rope_store(q, k, v, s.n_heads, s.n_kv_heads, s.head_dim,
-                           self.position.rotary_dim if table is not None else 0, table,
+                           getattr(self.position, "rotary_dim", 0) if table is not None else 0, table,
                            b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
                            step.status)
         return attend(q, s, step, view, out)

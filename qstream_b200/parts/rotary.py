@@ -25,8 +25,15 @@ class RotaryInterleaved(PositionEncoding):
         self.fused_table = table.contiguous().to(runtime.device) if self.rotary_dim > 0 else None
 
     def apply(self, q, k, step, n_heads, n_kv_heads, head_dim):
-        """Rotate q and k in place (no cache write); for mixers that do not fuse."""
-        raise NotImplementedError("attention fuses this rotation with its cache write")
+        """Rotate q and k in place (no cache write); for mixers that do not fuse the rotation with
+        their cache write.  A rotary width of 0 rotates nothing."""
+        if self.fused_table is None:
+            return
+        b = step.batch
+        for x, heads in ((q, n_heads), (k, n_kv_heads)):
+            if x is not None and heads > 0:
+                ops.rope_store(x, None, None, heads, 0, head_dim, self.rotary_dim, self.fused_table,
+                               b.tok_slot, b.tok_pos, None, 64, None, None, step.status)
 
 
 register("position", "rotary_interleaved", RotaryInterleaved)

@@ -5,7 +5,9 @@
 
 Compiles src/kernels_scalar.c, src/quant.c and src/sampling.c of the reference (CPU, gcc, no
 fast-math) into a shared object in a temporary folder, calls them through ctypes and writes
-the inputs' seeds and the outputs as JSON.  tests/test_plain.py compares the plain
+the inputs' seeds and the outputs as JSON.  The engine's rotary helper `apply_rope` is
+`static` (src/engine.c:205-234), so a one-line translation unit that includes src/engine.c
+and exports a wrapper is compiled beside them.  tests/test_plain.py compares the plain
 implementation of the tests with this file, so the comparison needs neither the reference
 nor a compiler at test time.  The reference's engine itself cannot serve as a model-level
 oracle: it has no GPT-J forward pass (sequential residual, full-head rotary, no biases,
@@ -14,6 +16,7 @@ formulas.
 """
 import ctypes
 import json
+import os
 import subprocess
 import sys
 import tempfile
@@ -31,6 +34,15 @@ def main(ref_root, out_path):
                                str(ref / "src/sampling.c"), "-lm", "-o", str(so)])
         lib = ctypes.CDLL(str(so))
         fp = ctypes.POINTER(ctypes.c_float)
+        shim_c = Path(tmp) / "rope_shim.c"
+        shim_c.write_text('#include "src/engine.c"\n'
+                          'void golden_apply_rope(float* q, float* k, int head_dim, int position, float theta,\n'
+                          '                       int num_heads, int num_kv_heads) {\n'
+                          '    apply_rope(q, k, head_dim, position, theta, num_heads, num_kv_heads);\n}\n')
+        shim_so = Path(tmp) / "librope_shim.so"
+        subprocess.check_call(["gcc", "-std=gnu11", "-O2", "-w", "-fPIC", "-shared", f"-I{ref / 'include'}", f"-I{ref}",
+                               str(shim_c), "-lm", "-o", str(shim_so)])
+        shim = ctypes.CDLL(str(shim_so), mode=os.RTLD_LAZY)      # the engine's other calls stay unresolved and unused
 
         def arr(a):
             a = np.array(a, dtype=np.float32, copy=True)      # the kernels work in place
@@ -104,6 +116,19 @@ def main(ref_root, out_path):
                 toks.append(int(lib.qsf_sample(xp, ctypes.c_int(64), ctypes.byref(cfg), ctypes.byref(r))))
             pipeline.append(dict(temperature=temperature, top_k=top_k, top_p=top_p, seed=seed, tokens=toks))
         out["sample"] = dict(logits=logits.tolist(), runs=pipeline)
+
+        # rotary: apply_rope(q, k, head_dim, position, theta, heads, kv heads) rotates the whole head in place
+        rope = []
+        for head_dim in (8, 32, 64):
+            for position in (0, 1, 63, 2047):
+                q, qp = arr(rng.normal(0, 1, 2 * head_dim))
+                k, kp = arr(rng.normal(0, 1, head_dim))
+                q0, k0 = q.copy(), k.copy()
+                shim.golden_apply_rope(qp, kp, ctypes.c_int(head_dim), ctypes.c_int(position), ctypes.c_float(10000.0),
+                                       ctypes.c_int(2), ctypes.c_int(1))
+                rope.append(dict(head_dim=head_dim, position=position, q=q0.tolist(), k=k0.tolist(),
+                                 q_out=q.tolist(), k_out=k.tolist()))
+        out["apply_rope"] = rope
 
     Path(out_path).write_text(json.dumps(out) + "\n")
     print(f"wrote {out_path} ({Path(out_path).stat().st_size} bytes)")

@@ -112,3 +112,68 @@ def test_context_is_the_limit(tmp_path):
     assert e.value.code == qs.QsError.INVALID_INPUT
     engine.cache.check()
     assert engine.cache.slots.n_free == engine.cache.slots.n_slots
+
+
+def plain_greedy(pcfg, w, prompt, n, stop=()):
+    return P.generate_greedy(pcfg, w, prompt, n, stop)
+
+
+def test_one_request_stops_while_the_others_go_on(tmp_path):
+    """Three requests in one batch, greedy, float32.  The stop token is taken from a free run so that
+    one request stops in mid-batch; a callback ends another a few tokens later; the third runs to its
+    length.  Every request's tokens must be what the plain model generates for it alone: a row
+    mix-up after a sequence leaves the batch would change the survivors' tokens."""
+    folder, cfg = make_folder(tmp_path, "B", "float32")
+    pcfg, w = P.load_model(folder)
+    rng = np.random.default_rng(23)
+    prompts = [random_tokens(rng, n, cfg.vocab_size) for n in (7, 20, 3)]
+    model = qs.load_model(folder, dtype="float32", device="cuda")
+    engine = qs.Engine(model, max_tokens=64 * 6, max_batch=3)
+    greedy = qs.SamplingConfig.greedy()
+    free = qs.generate(engine, prompts, max_new_tokens=14, sampling=greedy, stop_tokens=())
+    for prompt, got in zip(prompts, free.tokens):
+        assert got == plain_greedy(pcfg, w, prompt, 14)
+    # a token that request 1 emits fourth and that the other two do not emit before their ends
+    stop = free.tokens[1][3]
+    assert stop not in free.tokens[1][:3]
+    cut0 = free.tokens[0].index(stop) if stop in free.tokens[0] else 14
+    cut2 = free.tokens[2].index(stop) if stop in free.tokens[2] else 14
+    seen = []
+
+    def callback(i, tok):
+        seen.append((i, tok))
+        return i == 0 and len([1 for j, _ in seen if j == 0]) == 8      # ends request 0 after its eighth token
+    res = qs.generate(engine, prompts, max_new_tokens=14, sampling=greedy, stop_tokens=[stop], callback=callback)
+    assert res.tokens[1] == free.tokens[1][:3] and res.finish_reasons[1] == "stop"
+    want0 = free.tokens[0][:min(8, cut0)]
+    assert res.tokens[0] == want0 and res.finish_reasons[0] == ("callback" if cut0 >= 8 else "stop")
+    assert res.tokens[2] == free.tokens[2][:cut2] and res.finish_reasons[2] == ("length" if cut2 == 14 else "stop")
+    assert [t for i, t in seen if i == 2] == res.tokens[2]
+    engine.check_status()
+    engine.cache.check()
+    assert engine.cache.slots.n_free == engine.cache.slots.n_slots
+    # the stop token emitted, as the last token of the request it ends
+    res = qs.generate(engine, prompts, max_new_tokens=14, sampling=greedy, stop_tokens=[stop], emit_stop_token=True)
+    assert res.tokens[1] == free.tokens[1][:4] and res.finish_reasons[1] == "stop"
+
+
+def test_interrupt_from_a_callback(tmp_path):
+    folder, cfg = make_folder(tmp_path, "A", "bfloat16")
+    model = qs.load_model(folder, dtype="bfloat16", device="cuda")
+    engine = qs.Engine(model, max_tokens=64 * 4, max_batch=2)
+    gen = qs.Generator(engine)
+    calls = []
+
+    def callback(i, tok):
+        calls.append(i)
+        if len(calls) == 5:
+            gen.interrupt()
+    res = gen.generate([[1, 2, 3], [4, 5]], max_new_tokens=30, sampling=qs.SamplingConfig.greedy(), stop_tokens=(),
+                       callback=callback)
+    assert res.finish_reasons == ["interrupted", "interrupted"]
+    assert [len(t) for t in res.tokens] == [3, 3]          # the step in which the fifth token came is finished
+    engine.cache.check()
+    assert engine.cache.slots.n_free == engine.cache.slots.n_slots
+    # the engine serves the next call as if nothing had happened
+    res = gen.generate([[1, 2, 3]], max_new_tokens=4, sampling=qs.SamplingConfig.greedy(), stop_tokens=())
+    assert res.finish_reasons == ["length"] and len(res.tokens[0]) == 4

@@ -188,13 +188,17 @@ def test_attention_skips_padding():
     q, k, v, slot, pos = case.packed([(0, 0, 10)])
     slot[3] = -1
     tdev = case.table.cuda()
-    before = case.k_cache.clone()
     ops.rope_store(q, k, v, 2, 2, 16, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
     page = int(case.table[case.slots[0], 0])
     assert torch.isnan(case.k_cache[page, :, 3]).all() and not torch.isnan(case.k_cache[page, :, 2]).any()
     o = ops.attention(q, 2, 2, 16, 0.25, 0, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
     assert torch.equal(o[3], torch.zeros_like(o[3]))
-    assert before.shape == case.k_cache.shape
+    # nothing but the nine written rows of the sequence's own page has changed (the cache started as NaN)
+    others = [p for p in range(case.k_cache.shape[0]) if p != page]
+    assert torch.isnan(case.k_cache[others]).all() and torch.isnan(case.v_cache[others]).all()
+    assert torch.isnan(case.k_cache[page, :, 10:]).all() and torch.isnan(case.v_cache[page, :, 10:]).all()
+    written = [r for r in range(10) if r != 3]
+    assert torch.equal(case.k_cache[page][:, written].cpu(), case.k[0][written].transpose(0, 1))
 
 
 def test_argmax_lowest_index_wins_ties():
@@ -304,6 +308,33 @@ def test_decode_attention_kernel(H, Hkv, dh, window):
         ref = P.causal_attention(f64(case.q[i]), f64(case.k[i]), f64(case.v[i]), window)[-1]
         np.testing.assert_allclose(f64(got[j]), ref, atol=2e-2, rtol=2e-2, err_msg=f"length {lens[i]}")
         np.testing.assert_allclose(f64(got[j]), f64(gen[j]), atol=2e-2, rtol=2e-2)
+
+
+def test_decode_attention_finds_one_far_key():
+    """One key among a thousand matches the query and its value is a marker: the split kernel's output is
+    that marker when the key is visible (the first key, page and split edges, the window's first key) and
+    free of it when the key lies just outside the window."""
+    from qstream_b200.csrc import attention_bf16
+    H, dh, n = 2, 64, 1000
+    for far, window in ((0, 0), (63, 0), (64, 0), (255, 0), (256, 0), (999, 0), (700, 300), (699, 300), (744, 256)):
+        case = PagedCase("bfloat16", [n], H, H, dh, seed=far + window, fill=0.0)
+        case.q[0][:] = 0
+        case.k[0][:] = 0
+        case.q[0][n - 1, :, 0] = 12.0
+        case.k[0][far, :, 0] = 12.0
+        case.v[0][far] = 100.0
+        q, k, v, slot, pos = case.packed([(0, 0, n)])
+        tdev = case.table.cuda()
+        ops.rope_store(None, k, v, 0, H, dh, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+        o = attention_bf16.decode(q[n - 1:n], H, H, dh, dh ** -0.5, window, slot[n - 1:n], pos[n - 1:n], tdev, case.pt,
+                                  case.k_cache, case.v_cache, 1024, case.status)
+        got = f64(o[0]).reshape(H, dh)
+        if window == 0 or far > n - 1 - window:
+            np.testing.assert_allclose(got, np.full((H, dh), 100.0), atol=0.5, err_msg=f"key {far} window {window}")
+        else:                       # invisible: the mean of the window's values, none of them the marker
+            np.testing.assert_allclose(got, f64(case.v[0][n - window:n]).mean(0), atol=5e-2,
+                                       err_msg=f"key {far} window {window}")
+    assert int(case.status.item()) == 0
 
 
 def test_decode_attention_does_not_depend_on_the_batch():

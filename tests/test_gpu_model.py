@@ -142,3 +142,137 @@ def test_padding_changes_nothing(tmp_path, dtype):
     eng.cache.commit(batch.slots, batch.new_tokens)
     eng.check_status()
     assert torch.equal(plain, padded)
+
+
+@pytest.mark.parametrize("which,dtype", CASES)
+def test_mixed_steps_chunked_prompts_and_idle_sequences(tmp_path, which, dtype):
+    """Steps that are neither a batch of whole prompts nor one token each: a prompt in two chunks of
+    several tokens, a step in which one sequence brings a chunk and another a single token, a sequence
+    that brings nothing in a step, and more than eight live sequences decoded together (a captured
+    step of 16 rows with padding rows)."""
+    folder, cfg = make_folder(tmp_path, which, dtype)
+    eng = engine_for(folder, dtype, max_tokens=64 * 24, max_batch=12)
+    rng = np.random.default_rng(14)
+    lens = [70, 30, 9, 100, 5, 3, 2, 8, 1, 4]
+    reqs = [random_tokens(rng, n, cfg.vocab_size) for n in lens]
+    refs = [plain_logits(folder, r) for r in reqs]
+    slots = [eng.acquire() for _ in reqs]
+    got = [[] for _ in reqs]
+
+    def step(parts):
+        """parts: {request: (start, stop)}; logits at every place of every part."""
+        idx = sorted(parts)
+        out = eng.step([slots[i] for i in idx], [reqs[i][parts[i][0]:parts[i][1]] for i in idx],
+                       [all_places(parts[i][1] - parts[i][0]) for i in idx])
+        out = out.cpu().numpy() if out is not None else np.zeros((0, cfg.vocab_size))
+        row = 0
+        for i in idx:
+            n = parts[i][1] - parts[i][0]
+            got[i].append(out[row:row + n])
+            row += n
+
+    step({0: (0, 40), 1: (0, 29), 3: (0, 64)})                      # first chunks
+    step({0: (40, 69), 1: (29, 30), 2: (0, 9), 3: (64, 64)})        # chunk + one token + whole prompt + idle
+    step({0: (69, 70), 3: (64, 99), 4: (0, 5), 5: (0, 3), 6: (0, 1), 7: (0, 7), 8: (0, 1), 9: (0, 3)})
+    step({3: (99, 100), 6: (1, 2), 7: (7, 8), 9: (3, 4)})           # decode, 4 rows
+    eng.check_status()
+    eng.cache.check()
+    for i, ref in enumerate(refs):
+        assert_logits_close(np.concatenate(got[i]), ref, dtype, f"{which} {dtype} request {i}")
+    # ten sequences decode together: one more token each, fed as a decode step of ten rows
+    more = [random_tokens(rng, 1, cfg.vocab_size)[0] for _ in reqs]
+    keep = [i for i, n in enumerate(lens) if n < cfg.n_positions]
+    out = eng.step([slots[i] for i in keep], [[more[i]] for i in keep]).cpu().numpy()
+    eng.check_status()
+    for j, i in enumerate(keep):
+        ref = plain_logits(folder, reqs[i] + [more[i]])[-1:]
+        assert_logits_close(out[j:j + 1], ref, dtype, f"{which} {dtype} ten rows, request {i}")
+    for s in slots:
+        eng.release(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_page_that_held_inf_is_safe_for_its_next_owner(tmp_path, dtype):
+    """A request leaves values that are not finite in its pages; the next request gets those pages and
+    ends inside one of them: the rows past its end must not reach its result (0 * Inf would be NaN)."""
+    folder, cfg = make_folder(tmp_path, "A", dtype)
+    eng = engine_for(folder, dtype, max_tokens=128, max_batch=1)
+    rng = np.random.default_rng(15)
+    slot = eng.acquire()
+    eng.step([slot], [random_tokens(rng, 128, cfg.vocab_size)])
+    for g in eng.cache.groups:
+        g.k.fill_(float("inf"))
+        g.v.fill_(float("inf"))
+    eng.release(slot)
+    toks = random_tokens(rng, 70, cfg.vocab_size)
+    slot = eng.acquire()
+    got = eng.step([slot], [toks[:40]], [all_places(40)]).cpu().numpy()          # ends inside its first page
+    got2 = eng.step([slot], [toks[40:]], [all_places(30)]).cpu().numpy()         # a chunk that ends inside the second
+    eng.check_status()
+    eng.release(slot)
+    assert_logits_close(np.concatenate([got, got2]), plain_logits(folder, toks), dtype, f"{dtype} after Inf")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_check_nan_names_the_layer(tmp_path, dtype):
+    """An Inf planted in one weight of layer 1: with `check_nan` the step raises NAN_DETECTED naming
+    that layer (QStream src/engine.c:1176-1187); without it the step runs on."""
+    folder, cfg = make_folder(tmp_path, "B", dtype)
+    model = qs.load_model(folder, dtype=dtype, device="cuda")
+    eng = qs.Engine(model, qs.EngineConfig(max_tokens=256, max_batch=2, check_nan=True))
+    slot = eng.acquire()
+    assert eng.step([slot], [[1, 2, 3]]) is not None            # clean weights: no report
+    assert eng.step([slot], [[4]]) is not None                  # and none from a captured decode step
+    model.blocks[1].ffn.up_bias[5] = float("inf")
+    with pytest.raises(qs.QStreamError) as e:
+        eng.step([slot], [[5, 6]])
+    assert e.value.code == qs.QsError.NAN_DETECTED and "layer 1" in str(e.value)
+    with pytest.raises(qs.QStreamError) as e:                   # the decode graph carries the check too
+        eng.step([slot], [[7]])
+    assert e.value.code == qs.QsError.NAN_DETECTED and "layer 1" in str(e.value)
+    eng.release(slot)
+    quiet = qs.Engine(model, max_tokens=256, max_batch=2)
+    slot = quiet.acquire()
+    quiet.step([slot], [[5, 6]])
+    quiet.check_status()
+
+
+def test_rotary_dim_zero_means_no_rotation(tmp_path):
+    cfg = qs.GptjConfig.from_dict({**TINY["A"][0], "rotary_dim": 0, "architectures": ["GPTJForCausalLM"]})
+    folder = qs.write_model_folder(tmp_path / "norot", cfg, 4, "float32", TINY["A"][1])
+    eng = engine_for(folder, "float32")
+    toks = random_tokens(np.random.default_rng(16), 40, cfg.vocab_size)
+    slot = eng.acquire()
+    rows = [eng.step([slot], [toks[:33]], [all_places(33)]).cpu().numpy()]
+    rows += [eng.step([slot], [[t]]).cpu().numpy() for t in toks[33:]]
+    eng.check_status()
+    assert_logits_close(np.concatenate(rows), plain_logits(folder, toks), "float32", "rotary_dim 0")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_missing_page_is_reported_not_read(tmp_path, dtype):
+    """The device's page table names no page where a key should lie: every kernel skips the access and
+    sets a status code that `check_status` raises; nothing faults, and the engine works on afterwards."""
+    folder, cfg = make_folder(tmp_path, "A", dtype)
+    eng = engine_for(folder, dtype, max_tokens=256, max_batch=2)
+    rng = np.random.default_rng(17)
+    toks = random_tokens(rng, 80, cfg.vocab_size)
+    for cut in (80, 79):                                # a whole prompt; a prompt and then a decode step
+        slot = eng.acquire()
+        group = eng.cache.groups[0]
+        eng.step([slot], [toks[:cut - 10]])
+        eng.check_status()
+        group.table_dev[slot, 0] = -1                   # the first page's entry goes missing on the device
+        eng.step([slot], [toks[cut - 10:cut]])
+        if cut == 79:
+            eng.step([slot], [[toks[79]]])
+        with pytest.raises(qs.QStreamError) as e:
+            eng.check_status()
+        assert e.value.code == qs.QsError.INTERNAL and "page" in str(e.value)
+        group.table_dev[slot, 0] = int(group.table_host[slot, 0])
+        eng.release(slot)
+    slot = eng.acquire()
+    got = eng.step([slot], [toks], [all_places(80)]).cpu().numpy()
+    eng.check_status()                                  # the report was cleared with the error
+    assert_logits_close(got, plain_logits(folder, toks), dtype, f"{dtype} after the report")

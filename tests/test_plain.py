@@ -52,6 +52,28 @@ def test_filters_and_pipeline_match_the_reference():
         assert got == run["tokens"], run
 
 
+def test_rotary_matches_the_reference_engine():
+    """QStream's `apply_rope` (src/engine.c:205-234, run through a shim by the golden script) rotates the
+    whole head with frequency base^(-i / head_dim): the plain rotation with rotary_dim = head_dim is the
+    same function, and a partial rotation is that function on the first rotary_dim dims of a wider head.
+    The reference rounds the frequency to 32 bits before it multiplies by the position, so the angles
+    differ by up to position * 1e-7."""
+    for c in GOLDEN["apply_rope"]:
+        dh, pos = c["head_dim"], c["position"]
+        tol = 2e-6 + 4e-7 * pos
+        q = np.array(c["q"]).reshape(1, 2, dh)
+        k = np.array(c["k"]).reshape(1, 1, dh)
+        np.testing.assert_allclose(P.rotary_interleaved(q, [pos], dh).reshape(-1), c["q_out"], atol=tol, rtol=0)
+        np.testing.assert_allclose(P.rotary_interleaved(k, [pos], dh).reshape(-1), c["k_out"], atol=tol, rtol=0)
+        # partial: a head of 2 * dh dims of which the first dh are rotated
+        wide = np.concatenate([q, 7.0 + q], axis=-1)
+        out = P.rotary_interleaved(wide, [pos], dh)
+        np.testing.assert_allclose(out[..., :dh].reshape(-1), c["q_out"], atol=tol, rtol=0)
+        np.testing.assert_array_equal(out[..., dh:], wide[..., dh:])
+    moved = [c for c in GOLDEN["apply_rope"] if c["position"] == 63 and c["head_dim"] == 32][0]
+    assert np.abs(np.array(moved["q_out"]) - np.array(moved["q"])).max() > 0.1       # the case is not trivial
+
+
 def test_rotary_is_a_rotation_of_pairs():
     rng = np.random.default_rng(0)
     v = rng.normal(size=(6, 2, 16))

@@ -113,3 +113,100 @@ def test_random_weights_follow_the_named_distributions():
     assert abs(a["lm_head.bias"].std().item() - 0.01) < 0.002
     h = random_tensors(wanted, seed, torch.bfloat16, "cpu", scales)
     assert torch.equal(h["lm_head.weight"], a["lm_head.weight"].bfloat16())   # rounded once from float32
+
+
+def test_random_weights_are_a_function_of_seed_name_and_index():
+    """Counter-based: a tensor depends on the seed and its own name only, and any slice can be made alone."""
+    from qstream_b200.weights.loader import TensorDecl
+    from qstream_b200.weights.random_init import host_values, tensor_key
+    one = random_tensors({"a.weight": TensorDecl((40, 50))}, 5, torch.float32, "cpu")
+    two = random_tensors({"zzz": TensorDecl((3,), "bias"), "a.weight": TensorDecl((40, 50))}, 5, torch.float32, "cpu")
+    assert torch.equal(one["a.weight"], two["a.weight"])
+    key = tensor_key(5, "a.weight")
+    whole = host_values(key, "normal", 0.02, 0, 2000)
+    np.testing.assert_array_equal(host_values(key, "normal", 0.02, 700, 100), whole[700:800])
+    assert tensor_key(5, "a.weight") != tensor_key(5, "a.weighu") != tensor_key(6, "a.weight")
+    # the shape of a normal distribution, not only its first two moments
+    z = host_values(tensor_key(0, "shape"), "normal", 1.0, 0, 400000).astype(np.float64)
+    assert abs(z.mean()) < 0.01 and abs(z.std() - 1) < 0.01
+    assert abs((z ** 3).mean()) < 0.02 and abs((z ** 4).mean() - 3.0) < 0.06
+    for x, p in ((-2.0, 0.02275), (-1.0, 0.158655), (0.0, 0.5), (0.5, 0.691462), (1.5, 0.933193), (3.0, 0.99865)):
+        assert abs((z < x).mean() - p) < 0.003, x
+    u = host_values(tensor_key(0, "u"), "around_one", 0.25, 0, 100000)
+    assert 0.75 <= u.min() < 0.751 and 1.249 < u.max() < 1.25 and abs(u.mean() - 1) < 0.002
+    ints = host_values(tensor_key(0, "i"), "int", 5, 0, 10000)
+    assert ints.dtype == np.int32 and set(ints.tolist()) == {0, 1, 2, 3, 4}
+
+
+def test_a_checkpoint_in_two_files_with_an_index(tmp_path):
+    folder, cfg = make_folder(tmp_path, "B", "bfloat16")
+    wanted = declared_tensors(cfg.model_spec())
+    whole = SafetensorsFile(folder / "model.safetensors")
+    tensors = {n: whole.read(n).clone() for n in whole.names()}
+    whole.close()
+    (folder / "model.safetensors").unlink()
+    names = sorted(tensors)
+    shards = {"model-00001-of-00002.safetensors": names[:len(names) // 2],
+              "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    for fn, ns in shards.items():
+        write_safetensors(folder / fn, {n: tensors[n] for n in ns})
+    # without an index every *.safetensors file is opened
+    got = bind_tensors(open_checkpoint(folder), wanted, torch.bfloat16, "cpu")
+    assert all(torch.equal(got[n], tensors[n]) for n in names)
+    # with an index only the files it names are opened: a stray file beside them does no harm
+    index = {"metadata": {}, "weight_map": {n: fn for fn, ns in shards.items() for n in ns}}
+    (folder / "model.safetensors.index.json").write_text(json.dumps(index))
+    write_safetensors(folder / "optimizer.safetensors", {"step": torch.zeros(1)})
+    files = open_checkpoint(folder)
+    assert [f.path.name for f in files] == sorted(shards)
+    got = bind_tensors(files, wanted, torch.bfloat16, "cpu")
+    assert all(torch.equal(got[n], tensors[n]) for n in names)
+    # an index that points a tensor at the wrong file, or at a file that is not there
+    bad = dict(index["weight_map"])
+    bad[names[0]] = "model-00002-of-00002.safetensors"
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": bad}))
+    with pytest.raises(qs.QStreamError, match=names[0].replace(".", r"\.")):
+        open_checkpoint(folder)
+    bad[names[0]] = "model-00003-of-00002.safetensors"
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": bad}))
+    with pytest.raises(qs.QStreamError) as e:
+        open_checkpoint(folder)
+    assert e.value.code == qs.QsError.FILE_NOT_FOUND
+    (folder / "model.safetensors.index.json").write_text("{}")
+    with pytest.raises(qs.QStreamError) as e:
+        open_checkpoint(folder)
+    assert e.value.code == qs.QsError.FILE_CORRUPTED
+
+
+def test_fp32_matrices_in_a_bfloat16_engine(tmp_path, capsys):
+    folder, cfg = make_folder(tmp_path, "A", "float32")
+    wanted = declared_tensors(cfg.model_spec())
+    kept = bind_tensors(open_checkpoint(folder), wanted, torch.bfloat16, "cpu")
+    assert kept["lm_head.weight"].dtype == torch.float32
+    assert "stored in 32-bit" in capsys.readouterr().err
+    narrow = bind_tensors(open_checkpoint(folder), wanted, torch.bfloat16, "cpu", narrow_fp32_matrices=True)
+    assert narrow["lm_head.weight"].dtype == torch.bfloat16
+    assert torch.equal(narrow["lm_head.weight"], kept["lm_head.weight"].bfloat16())
+    assert narrow["lm_head.bias"].dtype == narrow["transformer.ln_f.weight"].dtype == torch.float32
+    assert "stored in 32-bit" not in capsys.readouterr().err
+
+
+def test_mkmodel_writes_the_folder_that_the_library_writes(tmp_path):
+    """`bin/qs-mkmodel` from a config.json and a seed: the same file as `write_model_folder`."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    cfg_dict, scales, seed = TINY["A"]
+    (tmp_path / "cfg.json").write_text(json.dumps({**cfg_dict, "architectures": ["GPTJForCausalLM"]}))
+    tool = Path(__file__).resolve().parent.parent / "bin" / "qs-mkmodel"
+    out = subprocess.run([sys.executable, str(tool), "--config", str(tmp_path / "cfg.json"), "--seed", str(seed),
+                          "--out", str(tmp_path / "made"), "--dtype", "bfloat16", "--matrix-std", str(scales.matrix_std),
+                          "--norm-spread", str(scales.norm_spread), "--bias-std", str(scales.bias_std)],
+                         capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    folder, cfg = make_folder(tmp_path, "A", "bfloat16")
+    assert (tmp_path / "made" / "model.safetensors").read_bytes() == (folder / "model.safetensors").read_bytes()
+    assert json.loads((tmp_path / "made" / "config.json").read_text())["n_embd"] == 64
+    bad = subprocess.run([sys.executable, str(tool), "--config", str(tmp_path / "nothing.json"), "--out", str(tmp_path / "x")],
+                         capture_output=True, text=True)
+    assert bad.returncode == 1 and "nothing.json" in bad.stderr

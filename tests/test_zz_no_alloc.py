@@ -4,8 +4,10 @@ Some callers of the kernel library cannot allocate device memory: they run insid
 memory plan, as a guest in a process whose allocator is not theirs, or in a region where
 cudaMalloc is forbidden.  For them `qs_attention_decode_static` keeps the scratch for the key
 splits in an array inside the library.  This test calls it twice in a row and compares each
-result with the ordinary entry point's, which takes the scratch from the caller; it also
-checks that a call beyond the array's size is refused.  It lives in a file that pytest
+result with the ordinary entry point's, which takes the scratch from the caller (the same
+kernels on the same inputs: the results must be equal bit for bit) and with plain attention in
+float64; it also checks that a call beyond the array's size is refused and that a position
+outside the stated bound is reported through the status word without any access.  It lives in a file that pytest
 collects last, so a run that stops at the first failure has run everything else first.
 """
 import ctypes
@@ -69,8 +71,44 @@ def test_static_scratch_matches_caller_scratch_twice():
         assert rc == 0, lib.qs_last_error()
         torch.cuda.synchronize()
         assert int(status.item()) == 0
-        np.testing.assert_allclose(got.float().cpu().numpy(), want.float().cpu().numpy(), atol=2e-2, rtol=2e-2)
-        assert torch.isfinite(got.float()).all()
+        assert torch.equal(got, want)
+        np.testing.assert_allclose(got.float().cpu().numpy(), _plain(q, kc, vc, table, lens, H, dh), atol=2e-2, rtol=2e-2)
+
+
+def _plain(q, kc, vc, table, lens, H, dh):
+    """softmax(q.k / sqrt(dh)) v over each sequence's keys, float64, from the pages its table row names."""
+    out = np.zeros((len(lens), H * dh))
+    kc, vc, q, table = kc.float().cpu().numpy().astype(np.float64), vc.float().cpu().numpy().astype(np.float64), \
+        q.float().cpu().numpy().astype(np.float64), table.cpu().numpy()
+    for s, n in enumerate(lens):
+        pages = table[s, :-(-n // 64)]
+        for h in range(H):
+            k = kc[pages, h].reshape(-1, dh)[:n]
+            v = vc[pages, h].reshape(-1, dh)[:n]
+            sc = k @ q[s, h * dh:(h + 1) * dh] / np.sqrt(dh)
+            w = np.exp(sc - sc.max())
+            out[s, h * dh:(h + 1) * dh] = (w / w.sum()) @ v
+    return out
+
+
+def test_a_position_outside_the_bound_is_reported_not_read():
+    """`tok_pos` must lie below max_context rounded up to 256: a larger one sets status 1, gives a row of
+    zeros and touches neither the cache nor the scratch beyond the call's share."""
+    lib = _library()
+    H, dh, ctx = 4, 64, 512
+    q, kc, vc, table, slot, pos = _case(9, [100, 200], H, dh)
+    pos[1] = 4000
+    out = torch.full((2, H * dh), float("nan"), dtype=torch.bfloat16).cuda()
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    rc = lib.qs_attention_decode_static(out.data_ptr(), H * dh, q.data_ptr(), H * dh, kc.data_ptr(), vc.data_ptr(),
+                                        table.data_ptr(), table.shape[1], 64, slot.data_ptr(), pos.data_ptr(),
+                                        2, H, H, dh, dh ** -0.5, 0, ctx, status.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.qs_last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1
+    assert (out[1].float() == 0).all()
+    np.testing.assert_allclose(out[:1].float().cpu().numpy(), _plain(q, kc, vc, table, [100], H, dh), atol=2e-2, rtol=2e-2)
 
 
 def test_static_scratch_refuses_what_does_not_fit():
