@@ -20,8 +20,8 @@ averaged over the run and at contexts 128, 1088 and 2048, each with its fraction
 bandwidth.  `codegen2b` and `codegen16b` are the two other benchmark shapes of the GPT-J
 architecture (16 prompts of unequal lengths with 256 decoded tokens each; a 2,048-token
 prefill and decode at batch 32 from 512-token prompts).  `--config` runs one shape alone;
-`--per-kernel` times each kernel of one layer by itself (CUDA events, many repeats, each
-repeat on another layer's weights so that nothing is served from L2) and prints a table of
+`--per-kernel` times each kernel of one layer by itself (CUDA events around a captured graph
+of many repeats, each repeat on another layer's weights so that nothing is served from L2) and prints a table of
 achieved GB/s or TFLOP/s against the measured peaks.
 
 Inputs are synthetic token ids, uniform over the vocabulary; each step reads more than
@@ -399,13 +399,19 @@ def per_kernel(shape, layers, pk, batch, ctx, repeats=56):
     rows = []
 
     def timed(name, fn, bytes_=0, flops=0):
+        # the repeats are captured into one CUDA graph, as a decode step is: the host's launch cost is not timed
         for i in range(3):
             fn(i % n_layer)
         torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(repeats):
+                fn(i % n_layer)
+        graph.replay()
+        torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for i in range(repeats):
-            fn(i % n_layer)
+        graph.replay()
         b.record()
         torch.cuda.synchronize()
         us = a.elapsed_time(b) * 1000.0 / repeats

@@ -7,12 +7,16 @@
 // row-major, weight rows = outputs, QStream's matvec convention
 // (include/qsf/kernels.h:53-58).  Each output element sums its K products in
 // ascending k inside one thread, so a row's result does not depend on M or on
-// which other rows are in the batch.
+// which other rows are in the batch.  The sum is taken in two levels: runs of 256
+// products in one accumulator, the runs' sums in a second one, so that the rounding
+// error grows with sqrt(256) + sqrt(K / 256) instead of sqrt(K) (at K = 16384 a
+// fifth of the single accumulator's error).
 #include "common.cuh"
 
 namespace {
 
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;   // 256 threads, 4x4 each
+constexpr int RUN_TILES = 16;                              // k-tiles per first-level run: 256 products
 
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
@@ -25,12 +29,13 @@ linear_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __res
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    float acc[TM][TN];
+    float acc[TM][TN], total[TM][TN];
 #pragma unroll
     for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < TN; ++j) { acc[i][j] = 0.f; total[i][j] = 0.f; }
 
+    int in_run = 0;
     for (int k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
         for (int e = tid; e < BM * BK; e += 256) {
@@ -57,6 +62,13 @@ linear_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __res
 #pragma unroll
                 for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
         }
+        if (++in_run == RUN_TILES) {                         // a run is complete: on to the second level
+            in_run = 0;
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) { total[i][j] += acc[i][j]; acc[i][j] = 0.f; }
+        }
         __syncthreads();
     }
 
@@ -68,7 +80,7 @@ linear_simt_kernel(TC* __restrict__ C, const TA* __restrict__ A, const TW* __res
         for (int j = 0; j < TN; ++j) {
             const int gn = n0 + tx * TN + j;
             if (gn >= N) continue;
-            float v = acc[i][j];
+            float v = total[i][j] + acc[i][j];
             if (bias) v += load_as_f32(bias, bias_dtype, gn);
             v = apply_activation(v, act);
             if (res1) v += to_f32(res1[(size_t)gm * ldr + gn]);
