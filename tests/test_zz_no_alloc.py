@@ -54,7 +54,7 @@ def _case(seed, lens, H, dh, n_pages=40):
 
 def test_static_scratch_matches_caller_scratch_twice():
     lib = _library()
-    H, dh, ctx = 4, 64, 512
+    H, dh, ctx = 4, 64, 4096
     stream = torch.cuda.current_stream().cuda_stream
     status = torch.zeros(1, dtype=torch.int32).cuda()
     for call, lens in enumerate(([300, 17, 512], [64, 450])):        # the second call reuses the array as the first left it
@@ -95,9 +95,9 @@ def test_a_position_outside_the_bound_is_reported_not_read():
     """`tok_pos` must lie below max_context rounded up to 256: a larger one sets status 1, gives a row of
     zeros and touches neither the cache nor the scratch beyond the call's share."""
     lib = _library()
-    H, dh, ctx = 4, 64, 512
+    H, dh, ctx = 4, 64, 4096
     q, kc, vc, table, slot, pos = _case(9, [100, 200], H, dh)
-    pos[1] = 4000
+    pos[1] = 5000
     out = torch.full((2, H * dh), float("nan"), dtype=torch.bfloat16).cuda()
     status = torch.zeros(1, dtype=torch.int32).cuda()
     rc = lib.qs_attention_decode_static(out.data_ptr(), H * dh, q.data_ptr(), H * dh, kc.data_ptr(), vc.data_ptr(),
