@@ -28,6 +28,7 @@ from ..errors import QsError, QStreamError
 from .pages import PagePool, SlotTable
 
 PAGE_TOKENS = 64
+CANARY = 0x5EED5EED
 
 
 @dataclass(frozen=True)
@@ -64,7 +65,8 @@ class KvGroup:
         self.page_tokens = page_tokens
         self.pool = PagePool(n_pages)
         self.max_pages = max_pages
-        shape = (len(self.entries), n_pages, need.n_kv_heads, page_tokens, need.head_dim)
+        # one page more than the pool hands out: every entry's last page holds guard words (`check_canaries`)
+        shape = (len(self.entries), n_pages + 1, need.n_kv_heads, page_tokens, need.head_dim)
         # Zeroed once here; a page that has been used is zeroed again (values only: scores of keys past
         # the end are replaced, not multiplied) when it is handed on to a step that leaves rows unwritten.
         self.k = torch.zeros(shape, dtype=dtype, device=device)
@@ -76,6 +78,23 @@ class KvGroup:
         self._dirty: set[int] = set()
         self.first_page = [0] * n_slots     # pages below this index were given back (window)
         self.held = [0] * n_slots           # pages held from first_page on (they are contiguous)
+        self.n_pages = n_pages
+        if self.k.is_cuda:
+            from ..csrc import ops
+            for store in (self.k, self.v):
+                for e in range(len(self.entries)):
+                    ops.canary_fill(store[e, n_pages], CANARY)
+
+    def damaged_guard_words(self) -> int:
+        """How many guard words behind the entries' pages no longer hold their pattern (0 on a host cache)."""
+        if not self.k.is_cuda:
+            return 0
+        from ..csrc import ops
+        damaged = torch.zeros(2, dtype=torch.int32, device=self.k.device)
+        for store in (self.k, self.v):
+            for e in range(len(self.entries)):
+                ops.canary_check(store[e, self.n_pages], CANARY, damaged)
+        return int(damaged[0].item())
 
     @property
     def bytes(self) -> int:
@@ -263,6 +282,13 @@ class SequenceCache:
     @property
     def bytes(self) -> int:
         return sum(g.bytes for g in self.groups) + self.state.bytes
+
+    def check_canaries(self) -> None:
+        """Device check: the guard page behind every cache entry's pages is as it was written."""
+        for g in self.groups:
+            n = g.damaged_guard_words()
+            if n:
+                raise QStreamError(QsError.INTERNAL, f"{n} guard words behind the cache pages of group {g.need} were overwritten")
 
     def check(self) -> None:
         """Host invariants: no slot or page lost, held twice or shared."""

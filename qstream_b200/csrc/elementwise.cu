@@ -97,58 +97,60 @@ __global__ void layernorm_kernel(T* __restrict__ out, const T* __restrict__ x,
     }
 }
 
-// The same for bfloat16 rows whose width is a multiple of 8: one warp per row, the row kept in
-// registers as NV 16-byte pieces per lane (width <= 256 * NV), statistics by warp butterflies.
+// The same for bfloat16 rows whose width is a multiple of 8: one block of 128 threads per row, the row
+// kept in registers as NV 16-byte pieces per thread (width <= 1024 * NV), all of a thread's loads in
+// flight at once, statistics by the block's fixed-order sum.  At 40 registers sixteen blocks share an SM,
+// so 2,048 rows are one wave.  (One warp per row with the whole row in a lane's registers, 160 of them,
+// moved 1.5 TB/s on 2,048 rows of 4,096.)
 template <int NV>
 __global__ void __launch_bounds__(128)
-layernorm_warp_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
-                      const void* __restrict__ w, int w_dtype, const void* __restrict__ b, int b_dtype,
-                      int rows, int D, float eps, size_t ldx, size_t ldo) {
+layernorm_row_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
+                     const void* __restrict__ w, int w_dtype, const void* __restrict__ b, int b_dtype,
+                     int D, float eps, size_t ldx, size_t ldo) {
+    __shared__ float scratch[33];
     grid_dep_launch();
     grid_dep_wait();
-    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    const int lane = threadIdx.x & 31;
-    const __nv_bfloat16* src = x + (size_t)row * ldx;
-    float v[NV][8];
+    const __nv_bfloat16* src = x + (size_t)blockIdx.x * ldx;
+    uint4 raw[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = (i * 128 + threadIdx.x) * 8;
+        raw[i] = c < D ? *reinterpret_cast<const uint4*>(src + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const int c = (i * 32 + lane) * 8;
-        if (c < D) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(src + c);
-            const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+        const uint32_t u[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { v[i][2 * j] = __uint_as_float(u[j] << 16); v[i][2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u); }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) s += v[i][j];
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
-        }
+        for (int j = 0; j < 4; ++j) s += __uint_as_float(u[j] << 16) + __uint_as_float(u[j] & 0xffff0000u);
     }
-    const float mean = warp_sum(s) / (float)D;
+    const float mean = block_sum(s, scratch) / (float)D;
     float q = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
-        if ((i * 32 + lane) * 8 < D) {
+        if ((i * 128 + threadIdx.x) * 8 < D) {
+            const uint32_t u[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; q += d * d; }
+            for (int j = 0; j < 4; ++j) {
+                const float d0 = __uint_as_float(u[j] << 16) - mean, d1 = __uint_as_float(u[j] & 0xffff0000u) - mean;
+                q += d0 * d0 + d1 * d1;
+            }
         }
-    const float rstd = 1.0f / sqrtf(warp_sum(q) / (float)D + eps);
-    __nv_bfloat16* dst = out + (size_t)row * ldo;
+    const float rstd = 1.0f / sqrtf(block_sum(q, scratch) / (float)D + eps);
+    __nv_bfloat16* dst = out + (size_t)blockIdx.x * ldo;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const int c = (i * 32 + lane) * 8;
+        const int c = (i * 128 + threadIdx.x) * 8;
         if (c < D) {
+            const uint32_t u[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
             uint32_t o[4];
             float wf[8], bf[8];
             load8_as_f32(w, w_dtype, c, wf);
             if (b) load8_as_f32(b, b_dtype, c, bf);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                float y0 = (v[i][2 * j] - mean) * rstd * wf[2 * j];
-                float y1 = (v[i][2 * j + 1] - mean) * rstd * wf[2 * j + 1];
+                float y0 = (__uint_as_float(u[j] << 16) - mean) * rstd * wf[2 * j];
+                float y1 = (__uint_as_float(u[j] & 0xffff0000u) - mean) * rstd * wf[2 * j + 1];
                 if (b) { y0 += bf[2 * j]; y1 += bf[2 * j + 1]; }
                 const __nv_bfloat162 pb = __floats2bfloat162_rn(y0, y1);
                 o[j] = *reinterpret_cast<const uint32_t*>(&pb);
@@ -163,15 +165,15 @@ QS_API int qs_layernorm(void* out, const void* x, int dtype, const void* w, int 
                         long long ldx, long long ldo, cudaStream_t stream) {
     if (rows == 0) return QS_OK;
     QS_REQUIRE(rows > 0 && D > 0, "layernorm: bad sizes rows=%d D=%d", rows, D);
-    // many rows: one warp per row (few rows are served faster by a whole block per row, below)
-    if (dtype == QS_BF16 && rows >= 256 && D % 8 == 0 && D <= 4096 && ldx % 8 == 0 && ldo % 8 == 0 &&
-        ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)w % 16) == 0 && (!b || ((uintptr_t)b % 16) == 0)) {
-        const int nv = (D + 255) / 256;
-        const int warps = 4;
-        const int blocks = (rows + warps - 1) / warps;
-#define GO(NV) qs_launch_dependent(layernorm_warp_kernel<NV>, dim3(blocks), dim3(warps * 32), 0, stream, (__nv_bfloat16*)out, \
-            (const __nv_bfloat16*)x, w, w_dtype, b, b_dtype, rows, D, eps, (size_t)ldx, (size_t)ldo)
-        if (nv <= 1) GO(1); else if (nv <= 2) GO(2); else if (nv <= 4) GO(4); else if (nv <= 8) GO(8); else GO(16);
+    // bfloat16 rows of 16-byte pieces: the row in registers, whatever the number of rows (prefill and decode
+    // steps then run the same arithmetic)
+    if (dtype == QS_BF16 && D % 8 == 0 && D <= 8192 && ldx % 8 == 0 && ldo % 8 == 0 &&
+        ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)w % (w_dtype == QS_F32 ? 32 : 16)) == 0 &&
+        (!b || ((uintptr_t)b % (b_dtype == QS_F32 ? 32 : 16)) == 0)) {
+        const int nv = (D + 1023) / 1024;
+#define GO(NV) qs_launch_dependent(layernorm_row_kernel<NV>, dim3(rows), dim3(128), 0, stream, (__nv_bfloat16*)out, \
+            (const __nv_bfloat16*)x, w, w_dtype, b, b_dtype, D, eps, (size_t)ldx, (size_t)ldo)
+        if (nv <= 1) GO(1); else if (nv <= 2) GO(2); else if (nv <= 4) GO(4); else GO(8);
 #undef GO
         return qs_check_launch("layernorm");
     }

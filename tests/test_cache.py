@@ -51,9 +51,9 @@ def test_groups_by_need_and_views():
     c = make_cache(window=100)
     assert len(c.groups) == 2                           # full and windowed layers have storage of their own
     full = [g for g in c.groups if g.need.window == 0][0]
-    assert full.entries == [0, 1] and full.k.shape == (2, 10, 2, 64, 16)
+    assert full.entries == [0, 1] and full.k.shape == (2, 10 + 1, 2, 64, 16)     # ten pages and the guard page
     v = c.view(1)
-    assert v.k.shape == (10, 2, 64, 16) and v.page_table.shape == (4, 4) and v.page_tokens == 64
+    assert v.k.shape == (11, 2, 64, 16) and v.page_table.shape == (4, 4) and v.page_tokens == 64
     assert c.view(2).need.window == 100
 
 

@@ -91,6 +91,7 @@ def test_unequal_batches_one_after_another(tmp_path, which, dtype):
             assert_logits_close(np.concatenate(got[i]), ref, dtype,
                                 f"{which} {dtype} batch {round_no} request {i}")
     assert eng.cache.slots.n_free == eng.cache.slots.n_slots
+    eng.cache.check_canaries()                          # nothing wrote behind the last cache page
 
 
 @pytest.mark.parametrize("which,dtype", CASES)
@@ -190,6 +191,10 @@ def test_mixed_steps_chunked_prompts_and_idle_sequences(tmp_path, which, dtype):
     for s in slots:
         eng.release(s)
     eng.cache.check()
+    eng.cache.check_canaries()
+    eng.cache.groups[0].v[1, -1, 0, 5, 3] = 0           # one element of a guard page
+    with pytest.raises(qs.QStreamError, match="guard words"):
+        eng.cache.check_canaries()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
