@@ -17,7 +17,8 @@ of the live sequences) with the measured copy bandwidth.
 `points` holds decode at batch 1 and 64 at context 2048, and, for batch 1, 8 and 64, a whole
 run from 128-token prompts until the context is full (1,920 steps): tokens per second
 averaged over the run and at contexts 128, 1088 and 2048, each with its fraction of the copy
-bandwidth.  `codegen2b` and `codegen16b` are the two other benchmark shapes of the GPT-J
+bandwidth; and the wall-clock time of a step with short prompts (1 x 128 and 8 x 64 tokens), replayed from
+a captured graph and, for comparison, launched kernel by kernel.  `codegen2b` and `codegen16b` are the two other benchmark shapes of the GPT-J
 architecture (16 prompts of unequal lengths with 256 decoded tokens each; a 2,048-token
 prefill and decode at batch 32 from 512-token prompts).  `--config` runs one shape alone;
 `--per-kernel` times each kernel of one layer by itself (CUDA events around a captured graph
@@ -303,6 +304,29 @@ class Bench:
         return {"value": round(T * 1000.0 / ms, 1), "tokens": T, "ms": round(ms, 3),
                 "frac": round(self.prefill_flops(lengths) / (ms * 1e-3) / (self.pk["bf16_tflops"] * 1e12), 4)}
 
+    def short_prompts(self, n_seq, length, use_graphs=True, repeats=9):
+        """Wall-clock milliseconds of one step with `n_seq` prompts of `length` tokens (host lists in, logits on
+        the device, the device awaited): what a caller waits for.  Steps of this size are bound by the host when
+        launched kernel by kernel; `use_graphs` replays them as one captured graph."""
+        torch, qs = self.torch, self.qs
+        engine = qs.Engine(self.model, max_tokens=n_seq * (-(-length // 64) * 64), max_batch=n_seq,
+                           max_context=length, use_graphs=use_graphs)
+        prompts = self.prompts([length] * n_seq)
+        times = []
+        for _ in range(repeats):
+            slots = [engine.acquire() for _ in range(n_seq)]
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            engine.step(slots, prompts)
+            torch.cuda.synchronize()
+            times.append((time.perf_counter() - t0) * 1e3)
+            for s in slots:
+                engine.release(s)
+        engine.check_status()
+        del engine
+        torch.cuda.empty_cache()
+        return sorted(times[2:])[len(times[2:]) // 2]
+
     # ------------------------------------------------------------------ through the Python entry point
     def end_to_end(self, batch, ctx, steps, settle=48):
         """`qstream_b200.generate` with host token lists in and out.  The timed region is the last `steps`
@@ -382,7 +406,7 @@ def run_codegen16b(sampler, pk, layers=0):
 
 # ----------------------------------------------------------------------------- each kernel alone
 
-def per_kernel(shape, layers, pk, batch, ctx, repeats=56):
+def per_kernel(shape, layers, pk, batch, ctx, prefill_tokens=2048, repeats=56):
     """Each kernel of one layer by itself, as the step calls it: CUDA events around `repeats` launches, each
     repeat on another layer's weights and cache entry so that nothing is served from L2."""
     import torch
@@ -420,7 +444,7 @@ def per_kernel(shape, layers, pk, batch, ctx, repeats=56):
         rows.append({"kernel": name, "us": round(us, 2), "GB/s": round(gbs, 1), "hbm_frac": round(gbs / pk["hbm_gbs"], 3),
                      "TFLOP/s": round(tfl, 1), "tc_frac": round(tfl / pk["bf16_tflops"], 3)})
 
-    for phase, T, lengths in (("decode", batch, [ctx - 1] * batch), ("prefill", 2048, [2048])):
+    for phase, T, lengths in (("decode", batch, [ctx - 1] * batch), ("prefill", prefill_tokens, [prefill_tokens])):
         engine = qs.Engine(model, max_tokens=sum(-(-(n + 1) // 64) * 64 for n in lengths), max_batch=len(lengths),
                            max_context=max(lengths) + 1, use_graphs=False)
         slots = [engine.acquire() for _ in lengths]
@@ -492,6 +516,7 @@ def main(argv=None) -> int:
     ap.add_argument("--config", default="gptj6b", choices=sorted(SHAPES), help="which benchmark shape (default: gptj6b)")
     ap.add_argument("--skip-points", action="store_true", help="the timed steps only: no other batch sizes, runs, prefill, e2e")
     ap.add_argument("--per-kernel", action="store_true", help="time each kernel of one layer by itself and print a table")
+    ap.add_argument("--prefill-tokens", type=int, default=2048, help="with --per-kernel: tokens of the prompt step")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()
@@ -505,7 +530,7 @@ def main(argv=None) -> int:
     torch.cuda.set_device(0)
     pk = peaks()
     if args.per_kernel:
-        return per_kernel(args.config, args.layers, pk, args.batch, args.context)
+        return per_kernel(args.config, args.layers, pk, args.batch, args.context, args.prefill_tokens)
     sampler = ClockSampler(0)
     if args.config != "gptj6b":
         fn = run_codegen2b if args.config == "codegen2b" else run_codegen16b
@@ -553,6 +578,10 @@ def main(argv=None) -> int:
             for c in (128, 1088, 2048):
                 points[f"run_b{b}_c{c}"] = round(r[f"c{c}"], 1)
                 points[f"run_b{b}_c{c}_hbm_frac"] = round(r[f"c{c}_frac"], 4)
+        # steps with short prompts: wall-clock, replayed from a captured graph and launched kernel by kernel
+        for n_seq, length in ((1, 128), (8, 64)):
+            points[f"prefill_{n_seq}x{length}_ms"] = round(bench.short_prompts(n_seq, length), 3)
+            points[f"prefill_{n_seq}x{length}_eager_ms"] = round(bench.short_prompts(n_seq, length, use_graphs=False), 3)
         line["points"] = points
         bench.close()
         del bench

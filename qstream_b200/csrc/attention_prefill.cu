@@ -97,6 +97,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // heads are the fast grid dimension and the tiles come longest first: CTAs start in order of falling
     // work, so the last ones to start are the shortest (a causal tile's work grows with its position)
     const TileInfo tile = tiles[blockIdx.y];
+    if (tile.n_rows <= 0) return;             // an unused entry of a tile list of fixed length (captured steps): the whole CTA leaves
     const int head = blockIdx.x;
     const int kvh = head / (n_heads / n_kv_heads);
     const int qpos_last = tile.qpos0 + tile.n_rows - 1;

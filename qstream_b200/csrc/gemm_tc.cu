@@ -247,8 +247,8 @@ __device__ __forceinline__ bool wait_or_abort_grid(uint64_t* bar, uint32_t parit
 template <int PAIR_BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const Epilogue ep, const int K, const int m_pairs, const int n_tiles,
-                    int32_t* __restrict__ status) {
+                    const Epilogue ep, const int K, const int m_pairs, const int n_tiles, const int splits,
+                    float* __restrict__ ws, int32_t* __restrict__ counters, int32_t* __restrict__ status) {
     constexpr int PAIR_STAGE = pair_stage<PAIR_BN>();
     constexpr int PAIR_STAGES = pair_stages<PAIR_BN>();
     constexpr uint32_t TMEM_COLS = 512;             // two accumulators of PAIR_BN columns; a power of two
@@ -260,12 +260,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint64_t* acc_empty = acc_full + 2;               // [2], the leader's counts both CTAs' epilogue threads
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* aborted = tmem_slot + 1;
+    volatile uint32_t* last_flag = tmem_slot + 2;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const int pair = blockIdx.x >> 1, n_pairs_grid = gridDim.x >> 1;
     const int num_kb = (K + BK - 1) / BK;
-    const int total_tiles = m_pairs * n_tiles;
+    // A work unit is a tile, or (splits > 1: fewer tiles than CTA pairs) one of `splits` equal parts of a
+    // tile's k-range; the parts of a tile are neighbouring units, so they run at the same time.
+    const int total_tiles = m_pairs * n_tiles * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -286,9 +289,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (elect_one()) {
             uint32_t it = 0;
             for (int t = pair; t < total_tiles && !*aborted; t += n_pairs_grid) {
-                const int m0 = (t % m_pairs) * 2 * BM + (int)rank * BM;
-                const int n0 = (t / m_pairs) * PAIR_BN + (int)rank * (PAIR_BN / 2);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int tile = t / splits, part = t - tile * splits;
+                const int m0 = (tile % m_pairs) * 2 * BM + (int)rank * BM;
+                const int n0 = (tile / m_pairs) * PAIR_BN + (int)rank * (PAIR_BN / 2);
+                const int kb_end = (int)((long long)(part + 1) * num_kb / splits);
+                for (int kb = (int)((long long)part * num_kb / splits); kb < kb_end; ++kb, ++it) {
                     const int s = it % PAIR_STAGES;
                     if (!wait_or_abort_grid(&empty[s], ((it / PAIR_STAGES) & 1) ^ 1, aborted, status)) { atomicExch(status, 151); *aborted = 1; break; }
                     uint8_t* st = smem + s * PAIR_STAGE;
@@ -307,7 +312,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int buf = i & 1;
                 if (!wait_or_abort_grid(&acc_empty[buf], ((i >> 1) & 1) ^ 1, aborted, status)) { atomicExch(status, 152); *aborted = 1; break; }
                 tc_fence_after_sync();
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int part = t % splits;
+                const int kb_begin = (int)((long long)part * num_kb / splits), kb_end = (int)((long long)(part + 1) * num_kb / splits);
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     const int s = it % PAIR_STAGES;
                     if (!wait_or_abort_grid(&full[s], (it / PAIR_STAGES) & 1, aborted, status)) { atomicExch(status, 153); *aborted = 1; break; }
                     tc_fence_after_sync();
@@ -316,7 +323,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint64_t db = smem_desc_sw128(a_addr + BM * BK * 2);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        mma_bf16_pair(tmem_base + (uint32_t)(buf * PAIR_BN), da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                        mma_bf16_pair(tmem_base + (uint32_t)(buf * PAIR_BN), da + 2 * k, db + 2 * k, idesc, kb != kb_begin || k != 0);
                     mma_commit_pair(&empty[s], 3);
                 }
                 mma_commit_pair(&acc_full[buf], 3);
@@ -333,16 +340,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int i = 0;
         for (int t = pair; t < total_tiles; t += n_pairs_grid, ++i) {
             const int buf = i & 1;
-            const int m = (t % m_pairs) * 2 * BM + (int)rank * BM + r, n0 = (t / m_pairs) * PAIR_BN;
+            const int tile = t / splits, part = t - tile * splits;
+            const int m = (tile % m_pairs) * 2 * BM + (int)rank * BM + r, n0 = (tile / m_pairs) * PAIR_BN;
             if (!wait_or_abort_grid(&acc_full[buf], (i >> 1) & 1, aborted, status)) { atomicExch(status, 154); *aborted = 1; break; }
             tc_fence_after_sync();
-#pragma unroll 1
-            for (int c = 0; c < PAIR_BN / 32; ++c) {
-                uint32_t raw[32];
-                tmem_load_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * PAIR_BN + c * 32), raw);
-                tmem_load_wait();
+            // bias, activation, residuals and the store of 32 columns of this thread's row
+            auto finish = [&](int c, const uint32_t (&raw)[32]) {
                 const int nc = n0 + c * 32;
-                if (m >= ep.M || nc >= ep.N) continue;
+                if (m >= ep.M || nc >= ep.N) return;
                 if (vec_ok && nc + 32 <= ep.N) {
                     __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(ep.C) + (size_t)m * ep.ldc + nc;
 #pragma unroll
@@ -386,9 +391,63 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int j = 0; j < 32; ++j)
                         if (nc + j < ep.N) store_out(ep, m, nc + j, __uint_as_float(raw[j]));
                 }
+            };
+            if (splits == 1) {
+#pragma unroll 1
+                for (int c = 0; c < PAIR_BN / 32; ++c) {
+                    uint32_t raw[32];
+                    tmem_load_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * PAIR_BN + c * 32), raw);
+                    tmem_load_wait();
+                    finish(c, raw);
+                }
+                tc_fence_before_sync();
+                mbar_arrive_cluster(leader_acc_empty[buf]);   // the leader's MMA warp waits for both CTAs' epilogues
+            } else {
+                // This CTA's 128 rows of the part's sums go to the workspace ([column][row]: a warp's stores are
+                // contiguous); a counter per (tile, CTA of the pair) tells the last part to arrive, which adds the
+                // parts in the order of their k-ranges and finishes the tile.  Nobody waits for anybody.
+                float* mine = ws + ((size_t)t * 2 + rank) * BM * PAIR_BN;
+#pragma unroll 1
+                for (int c = 0; c < PAIR_BN / 32; ++c) {
+                    uint32_t raw[32];
+                    tmem_load_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * PAIR_BN + c * 32), raw);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mine[(size_t)(c * 32 + j) * BM + r] = __uint_as_float(raw[j]);
+                }
+                tc_fence_before_sync();
+                mbar_arrive_cluster(leader_acc_empty[buf]);
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    const int prev = atomicAdd(&counters[tile * 2 + (int)rank], 1);
+                    const bool last = prev == splits - 1;
+                    *last_flag = last ? 1u : 0u;
+                    if (last) counters[tile * 2 + (int)rank] = 0;     // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*last_flag) {
+                    __threadfence();
+                    const float* first = ws + ((size_t)(tile * splits) * 2 + rank) * BM * PAIR_BN;
+#pragma unroll 1
+                    for (int c = 0; c < PAIR_BN / 32; ++c) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                        for (int p = 0; p < splits; ++p) {
+                            const float* src = first + (size_t)p * 2 * BM * PAIR_BN;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] += __ldcg(&src[(size_t)(c * 32 + j) * BM + r]);
+                        }
+                        uint32_t raw[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) raw[j] = __float_as_uint(v[j]);
+                        finish(c, raw);
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");        // last_flag is read by all before it is reused
+                (void)part;
             }
-            tc_fence_before_sync();
-            mbar_arrive_cluster(leader_acc_empty[buf]);   // the leader's MMA warp waits for both CTAs' epilogues
         }
     }
     tc_fence_before_sync();
@@ -789,6 +848,21 @@ int launch_stream(const void* W, const CUtensorMap& ma, const Epilogue& ep, int 
     return qs_check_launch("gemm_tc stream");
 }
 
+// Fewer tiles than CTA pairs (a few hundred tokens against a narrow N): each tile's k-range is cut into
+// equal parts for as many pairs as stand idle, at least 16 k-blocks each; their partial sums meet in the
+// workspace (see the kernel).  The cut depends on M, N, K and the device.
+long long pair_splits(long long tiles, int max_clusters, int K, int pair_bn, const float* ws, long long ws_floats,
+                      const int32_t* counters, int n_counters) {
+    if (!ws || !counters || tiles * 2 > max_clusters) return 1;
+    long long splits = max_clusters / tiles;
+
+    const long long most = ((K + BK - 1) / BK) / 16;
+    if (splits > most) splits = most;
+    if (splits > 3) splits = 3;            // measured at 256 x 4096 x 20480: 84, 61, 58, 66, 100 us with 1, 2, 3, 4, 6 parts
+    if (splits < 1 || tiles * 2 > n_counters || tiles * splits * 2 * BM * pair_bn > ws_floats) splits = 1;
+    return splits;
+}
+
 // The CTA-pair kernel as a cluster launch; 0 clusters means this device cannot run it at all.
 template <int PAIR_BN>
 int pair_max_clusters() {
@@ -813,14 +887,16 @@ int pair_max_clusters() {
 }
 
 template <int PAIR_BN>
-int launch_pair(const CUtensorMap& ma, const void* W, const Epilogue& ep, int M, int N, int K,
-                int32_t* status, cudaStream_t stream) {
+int launch_pair(const CUtensorMap& ma, const void* W, const Epilogue& ep, int M, int N, int K, float* ws,
+                long long ws_floats, int32_t* counters, int n_counters, int32_t* status, cudaStream_t stream) {
     const int max_clusters = pair_max_clusters<PAIR_BN>();
     CUtensorMap mw;
     int rc = tensor_map(&mw, W, N, K, K, PAIR_BN / 2);
     if (rc != QS_OK) return rc;
     const int m_pairs = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + PAIR_BN - 1) / PAIR_BN;
-    const long long total = (long long)m_pairs * n_tiles;
+    const long long tiles = (long long)m_pairs * n_tiles;
+    const long long splits = pair_splits(tiles, max_clusters, K, PAIR_BN, ws, ws_floats, counters, n_counters);
+    const long long total = tiles * splits;
     const int clusters = (int)(total < max_clusters ? total : max_clusters);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = pair_smem<PAIR_BN>(); cfg.stream = stream;
@@ -828,7 +904,8 @@ int launch_pair(const CUtensorMap& ma, const void* W, const Epilogue& ep, int M,
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<PAIR_BN>, ma, mw, ep, K, m_pairs, n_tiles, status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<PAIR_BN>, ma, mw, ep, K, m_pairs, n_tiles, (int)splits,
+                                       ws, counters, status);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc pair: %s", cudaGetErrorString(e));
     return qs_check_launch("gemm_tc pair");
 }
@@ -884,11 +961,18 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
                 // Tiles 192 wide where the rounds over the CTA pairs then cost less, a narrower tile's lower
                 // efficiency (measured: about a tenth) included: 384 tiles of 256 are 6 rounds over 74 pairs, the same
                 // matrix in 512 tiles of 192 is 7 rounds of three quarters the length.
+                // The cost of a width: rounds of work units over the pairs, times a unit's share of K, times the width.
                 const long long m_pairs = (M + 2 * BM - 1) / (2 * BM);
-                const long long r256 = (m_pairs * ((N + 255) / 256) + c256 - 1) / c256 * 256;
-                const long long r192 = c192 > 0 ? (m_pairs * ((N + 191) / 192) + c192 - 1) / c192 * 192 : r256;
-                if (r192 * 112 < r256 * 100) return launch_pair<192>(ma, W, ep, M, N, K, status, stream);
-                return launch_pair<256>(ma, W, ep, M, N, K, status, stream);
+                auto cost = [&](long long width, int pairs) {
+                    const long long tiles = m_pairs * ((N + width - 1) / width);
+                    const long long splits = pair_splits(tiles, pairs, K, (int)width, ws, ws_floats, counters, n_counters);
+                    return (tiles * splits + pairs - 1) / pairs * width * ((K + splits - 1) / splits);
+                };
+                const long long r256 = cost(256, c256);
+                const long long r192 = c192 > 0 ? cost(192, c192) : r256;
+                if (r192 * 112 < r256 * 100)
+                    return launch_pair<192>(ma, W, ep, M, N, K, ws, ws_floats, counters, n_counters, status, stream);
+                return launch_pair<256>(ma, W, ep, M, N, K, ws, ws_floats, counters, n_counters, status, stream);
             }
         }
         const int bn = N > 128 ? 256 : 128;

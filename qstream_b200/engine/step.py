@@ -141,6 +141,11 @@ class Engine:
         self.side_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.use_graphs = cfg.use_graphs and self.device.type == "cuda"
         self._graphs = {}
+        self._prefill_graphs = {}
+        self.graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None   # one pool: graphs never run at once
+        # steps with prompts are captured too if every part goes by device metadata alone
+        self.captures_prefill = self.use_graphs and all(getattr(b, "captures_any_step", False) for b in model.blocks) \
+            and getattr(model.final_norm, "captures_any_step", False)
         self._words_host = torch.zeros(9, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else None
         if verbose:
             import sys
@@ -242,8 +247,9 @@ class Engine:
         logits are asked for (default: the last).  Returns float32 logits [n_want, vocab] on
         the device, in the order of the sequences and of `want`; None if none is wanted.
 
-        The logits of a decode step (one token per sequence) are a view of a buffer that the
-        next decode step of the same batch size overwrites: copy what must outlive it."""
+        The logits of a captured step (one token per sequence; or at most 512 tokens for at most 8
+        sequences with the default `want`) are a view of a buffer that the next captured step of the
+        same size overwrites: copy what must outlive it."""
         if isinstance(tokens, TokenFeed):
             if not self.use_graphs:
                 host = tokens.buffer.tolist()
@@ -252,6 +258,10 @@ class Engine:
                 return self._finish(self._decode_step(slots, tokens, want))
         if self.use_graphs and len(tokens) > 0 and all(len(t) == 1 for t in tokens):
             return self._finish(self._decode_step(slots, tokens, want))
+        if self.captures_prefill:
+            done = self._captured_step(slots, tokens, want)
+            if done is not None:
+                return self._finish(done)
         batch = self.build_batch(slots, tokens, want)
         if batch.n_tokens == 0:
             return None
@@ -263,6 +273,33 @@ class Engine:
         if self.check_nan:
             self.check_status()
         return logits
+
+    def _captured_step(self, slots, tokens, want):
+        """A step with few tokens that wants each sequence's last logits only: replay the captured step of its
+        padded size (None: the step is not of that kind and runs kernel by kernel)."""
+        from .graphs import PrefillGraph, prefill_bucket
+        n_new = [len(t) for t in tokens]
+        if len(slots) != len(tokens) or not all(n_new):
+            return None
+        if want is not None and (len(want) != len(slots) or any(list(w) != [n - 1] for w, n in zip(want, n_new))):
+            return None
+        size = prefill_bucket(sum(n_new), len(slots))
+        if size is None:
+            return None
+        V = self.model.vocab_size
+        for s, toks in zip(slots, tokens):
+            for tok in toks:
+                if not 0 <= int(tok) < V:
+                    raise QStreamError(QsError.INVALID_INPUT,
+                                       f"token id {tok} (slot {s}) outside the vocabulary of {V}")
+        self.cache.prepare(slots, n_new)
+        p0 = [self.cache.length(s) for s in slots]
+        graph = self._prefill_graphs.get(size)
+        if graph is None:
+            graph = self._prefill_graphs[size] = PrefillGraph(self, *size)
+        logits = graph.run(slots, tokens, p0)
+        self.cache.commit(slots, n_new)
+        return logits[:len(slots)]
 
     def _decode_step(self, slots, tokens, want):
         """One token per sequence: replay the captured graph of the batch's size bucket."""

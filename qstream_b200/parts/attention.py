@@ -19,6 +19,8 @@ from .linear import linear
 
 
 class Attention(Mixer):
+    captures_any_step = True
+
     @classmethod
     def declare(cls, spec):
         hq, hkv = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim

@@ -59,6 +59,11 @@ class Runtime:
 
 class Part:
     role = ""
+    # True if `forward` takes everything that changes from step to step (which tokens, which sequences, how
+    # many of each) from the device tensors of `step.batch` and the cache, never from the batch's host lists:
+    # a step with prompts can then be captured once per padded size and replayed.  Decode steps are captured
+    # for every part; a part that leaves this False only makes steps with prompts run kernel by kernel.
+    captures_any_step = False
 
     @classmethod
     def declare(cls, spec) -> Mapping[str, TensorDecl]:

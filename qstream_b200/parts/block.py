@@ -15,12 +15,16 @@ from .base import Part, part_class, register
 class Arrangement(Part):
     role = "arrangement"
     norm_names: tuple = ()
+    captures_own_step = True            # the arrangements here read nothing of the step but `decode`
 
     def __init__(self, spec, parts, runtime):
         super().__init__(spec, {}, runtime)
         self.mixer = parts["mixer"]
         self.ffn = parts["ffn"]
         self.norms = parts["norms"]
+        position = getattr(self.mixer, "position", None)
+        self.captures_any_step = self.captures_own_step and all(
+            p.captures_any_step for p in (self.mixer, self.ffn, *self.norms.values(), *([position] if position else [])))
         missing = [n for n in self.norm_names if n not in self.norms]
         if missing:
             raise QStreamError(QsError.INVALID_MODEL,

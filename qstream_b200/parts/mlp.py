@@ -12,6 +12,8 @@ from .linear import linear
 
 
 class Mlp(FeedForward):
+    captures_any_step = True
+
     @classmethod
     def declare(cls, spec):
         d = {"up": TensorDecl((spec.inner, spec.width)), "down": TensorDecl((spec.width, spec.inner))}

@@ -7,6 +7,8 @@ from .base import Norm, register
 
 
 class LayerNorm(Norm):
+    captures_any_step = True
+
     @classmethod
     def declare(cls, spec):
         d = {"weight": TensorDecl((spec.size,), "norm_weight")}

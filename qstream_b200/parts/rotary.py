@@ -14,6 +14,8 @@ from .base import PositionEncoding, register
 
 
 class RotaryInterleaved(PositionEncoding):
+    captures_any_step = True
+
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
         self.rotary_dim = int(spec.rotary_dim)

@@ -99,3 +99,26 @@ def test_split_k_is_exact_and_does_not_depend_on_the_batch(N, K):
         part = gemm_tc.linear(x[rows], w, bias, "gelu_new", (res[rows],), torch.float32)
         assert torch.equal(part, whole[rows]), rows
     gemm_tc.check_status(x.device)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 4096, 20480), (512, 4096, 20480), (300, 520, 16384), (700, 1000, 8192),
+                                   (129, 256, 2048), (400, 4096, 4096)])
+def test_cta_pairs_cut_along_k(M, N, K):
+    """A few hundred tokens against a narrow N give fewer tiles than CTA pairs: the tiles' k-ranges are cut
+    for the idle pairs, the parts meet in a workspace and the last to arrive adds them in order and runs the
+    epilogue.  Against float64, with bias, activation and residual; the same bits on every call."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16().cuda()
+    bias = torch.randn(N, generator=g).bfloat16().cuda()
+    res = torch.randn(M, N, generator=g).bfloat16().cuda()
+    ref = P.gelu_new(f64(x) @ f64(w).T + f64(bias)) + f64(res)
+    got = gemm_tc.linear(x, w, bias, "gelu_new", (res,), torch.float32)
+    np.testing.assert_allclose(f64(got), ref, atol=3e-3, rtol=3e-3)
+    for _ in range(3):
+        assert torch.equal(gemm_tc.linear(x, w, bias, "gelu_new", (res,), torch.float32), got)
+    got16 = gemm_tc.linear(x, w, bias, "gelu_new", (res,))
+    np.testing.assert_allclose(f64(got16), ref, atol=3e-2, rtol=1e-2)
+    plain = gemm_tc.linear(x, w, out_dtype=torch.float32)
+    np.testing.assert_allclose(f64(plain), f64(x) @ f64(w).T, atol=2e-3, rtol=2e-3)
+    gemm_tc.check_status(x.device)

@@ -281,3 +281,43 @@ def test_a_missing_page_is_reported_not_read(tmp_path, dtype):
     got = eng.step([slot], [toks], [all_places(80)]).cpu().numpy()
     eng.check_status()                                  # the report was cleared with the error
     assert_logits_close(got, plain_logits(folder, toks), dtype, f"{dtype} after the report")
+
+
+@pytest.mark.parametrize("which,dtype", CASES)
+def test_captured_steps_with_prompts(tmp_path, which, dtype):
+    """Steps of up to 512 tokens for up to 8 sequences that want last logits only are captured once per
+    padded size and replayed: the same graph serves other lengths, other slots and continuations of
+    sequences that already hold tokens, and gives what the kernel-by-kernel step gives."""
+    folder, cfg = make_folder(tmp_path, which, dtype)
+    eng = engine_for(folder, dtype, max_tokens=64 * 40, max_batch=8)
+    assert eng.captures_prefill
+    rng = np.random.default_rng(18)
+    limit = cfg.n_positions
+    rounds = [[5], [64], [70, 3], [9, 100, 33], [2, 2, 2, 2, 2], [60, 1, 17, 40, 8, 8, 30, 12], [5], [120, 90]]
+    for lens in rounds:
+        lens = [min(n, limit - 20) for n in lens]
+        reqs = [random_tokens(rng, n + 12, cfg.vocab_size) for n in lens]
+        slots = [eng.acquire() for _ in reqs]
+        got = [[] for _ in reqs]
+        out = eng.step(slots, [r[:n] for r, n in zip(reqs, lens)]).cpu().numpy()        # captured: default want
+        for i in range(len(reqs)):
+            got[i].append(out[i:i + 1])
+        # a second chunk of unequal sizes on top (positions do not start at 0), again captured
+        more = [1 + (i * 5) % 11 for i in range(len(reqs))]
+        out = eng.step(slots, [r[n:n + m] for r, n, m in zip(reqs, lens, more)]).cpu().numpy()
+        for i in range(len(reqs)):
+            got[i].append(out[i:i + 1])
+        eng.check_status()
+        for i, (r, n, m) in enumerate(zip(reqs, lens, more)):
+            ref = plain_logits(folder, r[:n + m])
+            assert_logits_close(np.concatenate(got[i]), ref[[n - 1, n + m - 1]], dtype, f"{which} {dtype} lens {lens} request {i}")
+        for s in slots:
+            eng.release(s)
+    assert len(eng._prefill_graphs) >= 3
+    eng.cache.check()
+    # the same step kernel by kernel gives the same bits (same kernels, same order of sums)
+    plain_eng = qs.Engine(eng.model, max_tokens=64 * 8, max_batch=4, use_graphs=False)
+    toks = [random_tokens(rng, n, cfg.vocab_size) for n in (33, 7)]
+    a = [eng.acquire(), eng.acquire()]
+    b = [plain_eng.acquire(), plain_eng.acquire()]
+    assert torch.equal(eng.step(a, toks), plain_eng.step(b, toks))
