@@ -234,7 +234,8 @@ class Bench:
         which tokens per second are reported (the window that starts there, or the last one)."""
         torch, qs = self.torch, self.qs
         engine = qs.Engine(self.model, max_tokens=batch * ctx, max_batch=batch, max_context=ctx)
-        warm = [engine.acquire() for _ in range(batch)]            # capture the graph of this batch size first
+        engine.capture_decode_graphs([batch])                      # every graph the run will replay, before the clock starts
+        warm = [engine.acquire() for _ in range(batch)]
         step = self._decoder(engine, warm, self._prefill_all(engine, warm, self.prompts([8] * batch)))
         for _ in range(4):
             step()
@@ -336,6 +337,7 @@ class Bench:
         qs = self.qs
         from qstream_b200.engine.graphs import bucket_for
         engine = qs.Engine(self.model, max_tokens=batch * ctx, max_batch=batch, max_context=ctx)
+        engine.capture_decode_graphs([batch])
         greedy = qs.SamplingConfig.greedy()
         qs.generate(engine, self.prompts([64] * batch), max_new_tokens=4, sampling=greedy, stop_tokens=())
         total = settle + steps
@@ -367,6 +369,7 @@ class Bench:
         engine = qs.Engine(self.model, max_tokens=sum(-(-(n + new_tokens) // 64) * 64 for n in lengths), max_batch=batch,
                            max_context=ctx)
         greedy = qs.SamplingConfig.greedy()
+        engine.capture_decode_graphs([batch])
         qs.generate(engine, self.prompts([16] * batch), max_new_tokens=4, sampling=greedy, stop_tokens=())
         res = qs.generate(engine, self.prompts(lengths), max_new_tokens=new_tokens, sampling=greedy, stop_tokens=())
         assert all(len(t) == new_tokens for t in res.tokens)

@@ -82,8 +82,11 @@ def attend(q, spec, step, view, out=None):
     b = step.batch
     if (b.decode and view.page_tokens == 64 and spec.head_dim % 8 == 0 and spec.head_dim <= 512
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+        # the grid covers the longest sequence of the step (a captured step: the bound it was captured for),
+        # not the longest the cache allows: splits beyond it would be CTAs that start only to leave
+        reach = min(b.max_total or step.cache.max_context, step.cache.max_context)
         return decode(q, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.scale, spec.window, b.tok_slot,
-                      b.tok_pos, view.page_table, view.page_tokens, view.k, view.v, step.cache.max_context,
+                      b.tok_pos, view.page_table, view.page_tokens, view.k, view.v, reach,
                       step.status, out=out)
     if (not b.decode and b.slots and view.page_tokens == 64 and spec.head_dim % 16 == 0 and spec.head_dim <= 256
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):

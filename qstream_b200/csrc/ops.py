@@ -44,6 +44,7 @@ _SIGNATURES = {
     "qs_check_finite": ([c_void_p, c_int, c_int, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p], c_int),
     "qs_canary_fill": ([c_void_p, c_longlong, c_uint, c_void_p], c_int),
     "qs_canary_check": ([c_void_p, c_longlong, c_uint, c_void_p, c_void_p], c_int),
+    "qs_selftest_bounded_wait": ([c_void_p, c_int, c_void_p], c_int),
     "qs_take_tokens": ([c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p], c_int),
     "qs_zero_pages": ([c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p], c_int),
 }
@@ -332,3 +333,9 @@ def zero_pages(storage: torch.Tensor, pages: torch.Tensor) -> None:
     page_bytes = storage.stride(1) * storage.element_size()
     check(library().qs_zero_pages(ptr(storage), storage.stride(0) * storage.element_size(), page_bytes,
                                   storage.shape[0], _int32(pages, "pages"), pages.numel(), storage.shape[1], stream()))
+
+
+def selftest_bounded_wait(status: torch.Tensor, polls: int = 2000) -> None:
+    """Launch a kernel that waits, with the library's polling loop, on a barrier nothing completes: after
+    `polls` polls it records code 199 in `status` (int32 on the device) and returns."""
+    check(library().qs_selftest_bounded_wait(_int32(status, "status"), int(polls), stream()))

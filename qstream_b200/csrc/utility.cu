@@ -5,6 +5,7 @@
 // its arena has no guard words.  Each kernel here has a host twin with the same
 // arithmetic (weights/random_init.py for the generator; numpy in the tests).
 #include "common.cuh"
+#include "sm100.cuh"
 
 // ----------------------------------------------------------------------------- random fill
 //
@@ -294,4 +295,31 @@ QS_API int qs_zero_pages(void* base, long long entry_bytes, long long page_bytes
     zero_pages_kernel<<<dim3(n_pages, n_entries, z), 256, 0, stream>>>((uint8_t*)base, (size_t)entry_bytes,
                                                                      (size_t)page_bytes, pages, n_total_pages);
     return qs_check_launch("zero pages");
+}
+
+// ----------------------------------------------------------------------------- the bounded wait, by itself
+
+// A wait on a barrier that nothing will ever complete, with the polling loop that every kernel of the
+// library uses (sm100::mbar_try_wait under a limit): after `polls` polls it gives up, records code 199
+// in `status` and returns.  The context stays usable.  For tests of the path a kernel takes when one of its
+// waits runs out; no kernel of the model calls this.
+__global__ void bounded_wait_selftest_kernel(int32_t* __restrict__ status, uint32_t polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(&bar, 1);
+        sm100::mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        bool done = false;
+        for (uint32_t i = 0; i < polls && !done; ++i) done = sm100::mbar_try_wait(&bar, 0);
+        if (!done) atomicExch(status, 199);
+    }
+    __syncthreads();
+}
+
+QS_API int qs_selftest_bounded_wait(int32_t* status, int polls, cudaStream_t stream) {
+    QS_REQUIRE(status != nullptr && polls > 0 && polls <= (1 << 16), "bounded wait self-test: polls=%d", polls);
+    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, (uint32_t)polls);
+    return qs_check_launch("bounded wait self-test");
 }

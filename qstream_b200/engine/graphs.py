@@ -28,12 +28,22 @@ def bucket_for(n: int) -> int:
     return -(-n // 64) * 64
 
 
-class DecodeGraph:
-    """One captured decode step for `rows` packed rows."""
+REACH_STEP = 256                # a decode graph serves sequences of up to a multiple of this many tokens
 
-    def __init__(self, engine, rows: int):
+
+def reach_for(longest: int, max_context: int) -> int:
+    """The bound on the longest sequence that a decode graph is captured for: the attention kernels' grids
+    cover splits of 256 keys up to it, so a graph for short sequences launches no CTAs for keys nobody has."""
+    return min(-(-max(longest, 1) // REACH_STEP) * REACH_STEP, -(-max_context // REACH_STEP) * REACH_STEP)
+
+
+class DecodeGraph:
+    """One captured decode step for `rows` packed rows whose sequences hold at most `reach` tokens."""
+
+    def __init__(self, engine, rows: int, reach: int = 0):
         self._engine = weakref.ref(engine)          # the engine owns its graphs, not the other way round
         self.rows = rows
+        self.reach = reach
         dev = engine.device
         sizes = [rows, rows, rows, rows, rows, rows + 1, rows, rows]        # the last: where a fed token comes from
         self.offs = np.concatenate([[0], np.cumsum(sizes)]).astype(int)
@@ -54,7 +64,7 @@ class DecodeGraph:
         self.meta.copy_(self.staging[0])
         self.batch = StepBatch(n_seq=rows, n_tokens=rows, n_want=rows, tokens=v[0], tok_slot=v[1], tok_pos=v[2],
                                want_rows=v[3], seq_slot=v[4], seq_start=v[5], seq_p0=v[6],
-                               slots=[], new_tokens=[1] * rows, p0=[], decode=True, max_new=1, max_total=0)
+                               slots=[], new_tokens=[1] * rows, p0=[], decode=True, max_new=1, max_total=reach)
         self.graph = None
         self.logits = None
         self.launches = 0

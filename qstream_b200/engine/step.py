@@ -104,6 +104,7 @@ STATUS_MESSAGES = {
     1: "a token's position lies outside the position table",
     2: "a token was to be written to a cache page its sequence does not hold",
     3: "attention met a cache page its sequence does not hold",
+    199: "the self-test's wait ran out, as it must",
 }
 
 
@@ -304,7 +305,7 @@ class Engine:
     def _decode_step(self, slots, tokens, want):
         """One token per sequence: replay the captured graph of the batch's size bucket."""
         from ..csrc import ops
-        from .graphs import DecodeGraph, bucket_for
+        from .graphs import DecodeGraph, bucket_for, reach_for
         n = len(slots)
         fed = isinstance(tokens, TokenFeed)
         if (len(tokens.rows) if fed else len(tokens)) != n or (want is not None and len(want) != n):
@@ -330,9 +331,10 @@ class Engine:
         self.cache.prepare(slots, ones)
         p0 = [self.cache.length(s) for s in slots]
         rows = bucket_for(n)
-        graph = self._graphs.get(rows)
+        reach = reach_for(max(p0) + 1, self.cache.max_context)
+        graph = self._graphs.get((rows, reach))
         if graph is None:
-            graph = self._graphs[rows] = DecodeGraph(self, rows)
+            graph = self._graphs[rows, reach] = DecodeGraph(self, rows, reach)
         logits = graph.run(slots, toks, p0)
         self.cache.commit(slots, ones)
         if want is None or all(len(w) == 1 for w in want):
@@ -341,6 +343,23 @@ class Engine:
         if not picked:
             return None
         return self.rows_of(logits, picked)
+
+    def capture_decode_graphs(self, batch_sizes: Sequence[int]) -> int:
+        """Capture, ahead of their first use, the decode graphs of the given batch sizes for every length a
+        sequence can reach (a graph is otherwise captured when a step first needs it, which costs that
+        step some tens of milliseconds).  Returns how many graphs were captured."""
+        from .graphs import DecodeGraph, REACH_STEP, bucket_for, reach_for
+        if not self.use_graphs:
+            return 0
+        made = 0
+        for n in sorted({bucket_for(int(b)) for b in batch_sizes}):
+            for longest in range(REACH_STEP, self.cache.max_context + REACH_STEP, REACH_STEP):
+                key = (n, reach_for(longest, self.cache.max_context))
+                if key not in self._graphs:
+                    self._graphs[key] = DecodeGraph(self, *key)
+                    self._graphs[key].capture()
+                    made += 1
+        return made
 
     def rows_of(self, logits: torch.Tensor, rows: Sequence[int]) -> torch.Tensor:
         """The listed rows of a logits tensor, as a new tensor."""
@@ -376,6 +395,6 @@ class Engine:
                                f"row {nan[2]} of the step, element {nan[3]}")
         if gemm:
             raise QStreamError(QsError.INTERNAL, f"tensor-core matrix product: a wait inside the kernel ran out (code {gemm})")
-        if code >= 100:
+        if 100 <= code < 199:
             raise QStreamError(QsError.INTERNAL, f"attention: a wait inside the kernel ran out (code {code})")
         raise QStreamError(QsError.INTERNAL, STATUS_MESSAGES.get(code, f"kernel status {code}"))

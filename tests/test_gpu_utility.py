@@ -109,3 +109,27 @@ def test_take_tokens_and_zero_pages():
     store = torch.ones(3, 5, 2, 64, 16, dtype=torch.bfloat16).cuda()
     ops.zero_pages(store, torch.tensor([4, 1], dtype=torch.int32).cuda())
     assert (store[:, [1, 4]] == 0).all() and (store[:, [0, 2, 3]] == 1).all()
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_usable(tmp_path):
+    """The library's bounded wait on a barrier that nothing completes: it gives up after its polls, the kernel
+    records a status code and returns; the host reads the code through the engine's `check_status`, and the
+    next step runs as if nothing had happened.  (No kernel of the model is made to fail for this.)"""
+    from util import make_folder
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    ops.selftest_bounded_wait(status, polls=500)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 199
+    folder, cfg = make_folder(tmp_path, "A", "bfloat16")
+    eng = qs.Engine(qs.load_model(folder, dtype="bfloat16", device="cuda"), max_tokens=128, max_batch=1)
+    slot = eng.acquire()
+    first = eng.step([slot], [[1, 2, 3]]).clone()
+    eng.check_status()
+    ops.selftest_bounded_wait(eng.status, polls=500)
+    with pytest.raises(qs.QStreamError) as e:
+        eng.check_status()
+    assert e.value.code == qs.QsError.INTERNAL and "ran out" in str(e.value)
+    eng.release(slot)
+    slot = eng.acquire()
+    assert torch.equal(eng.step([slot], [[1, 2, 3]]), first)
+    eng.check_status()
