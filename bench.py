@@ -147,7 +147,7 @@ class Bench:
         self.rng = np.random.default_rng(seed)
         c = self.cfg
         self.kv_bytes_per_token = 2 * c.n_layer * c.n_embd * 2
-        self.weight_bytes = self.model.weight_bytes - self.model.wte.numel() * 2    # every weight a step reads
+        self.weight_bytes = self.model.weight_bytes - self.model.embedding_bytes    # every weight a step reads
 
     def close(self):
         self.model = None
@@ -490,8 +490,8 @@ def per_kernel(shape, layers, pk, batch, ctx, prefill_tokens=2048, repeats=56):
               bytes_=(D + F) * D * 2, flops=2 * T * (D + F) * D)
         if phase == "decode":
             z = torch.randn(T, D, device="cuda", generator=rng).bfloat16()
-            logits = linear(z, model.head_weight, model.head_bias, out_dtype=torch.float32)
-            timed(f"{tag} lm_head product", lambda i: linear(z, model.head_weight, model.head_bias, out_dtype=torch.float32),
+            logits = model.head.forward(z)
+            timed(f"{tag} lm_head product", lambda i: model.head.forward(z),
                   bytes_=V * D * 2, flops=2 * T * D * V)
             timed(f"{tag} argmax", lambda i: ops.argmax(logits), bytes_=T * V * 4)
         engine.check_status()

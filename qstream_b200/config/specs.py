@@ -122,11 +122,11 @@ class ModelSpec:
     vocab_size: int
     width: int
     max_positions: int
-    embedding: EmbeddingSpec
+    embedding: object
     layers: Tuple[BlockSpec, ...]
     schedule: Tuple[LayerRun, ...]
-    final_norm: object
-    head: HeadSpec
+    final_norm: Optional[object]            # None: the head sees the last layer's output as it is
+    head: object
     stop_tokens: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
 

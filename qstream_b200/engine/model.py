@@ -20,7 +20,6 @@ from ..config import ModelSpec, load_config
 from ..csrc import ops
 from ..errors import QsError, QStreamError
 from ..parts import Runtime, build_block, part_class
-from ..parts.linear import linear
 from ..weights.loader import TensorDecl, bind_tensors, open_checkpoint
 from ..weights.random_init import InitScales, random_tensors
 
@@ -37,16 +36,14 @@ def resolve_dtype(dtype) -> torch.dtype:
 
 def _part_declarations(spec: ModelSpec):
     """Yield (part spec, {own name: TensorDecl}) for every part that holds tensors."""
-    yield spec.embedding, {"weight": TensorDecl((spec.embedding.vocab_size, spec.embedding.width))}
+    yield spec.embedding, part_class("embedding", spec.embedding.kind).declare(spec.embedding)
     for block in spec.layers:
         for role, ps in (("mixer", block.mixer), ("feed_forward", block.ffn),
                          *(("norm", n) for n in block.norms.values())):
             yield ps, part_class(role, ps.kind).declare(ps)
-    yield spec.final_norm, part_class("norm", spec.final_norm.kind).declare(spec.final_norm)
-    head = {} if spec.head.tied else {"weight": TensorDecl((spec.head.vocab_size, spec.head.width))}
-    if spec.head.bias:
-        head["bias"] = TensorDecl((spec.head.vocab_size,), "bias")
-    yield spec.head, head
+    if spec.final_norm is not None:
+        yield spec.final_norm, part_class("norm", spec.final_norm.kind).declare(spec.final_norm)
+    yield spec.head, part_class("head", spec.head.kind).declare(spec.head)
 
 
 def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
@@ -77,16 +74,26 @@ class CausalLM:
         def tensors_of(part_spec, decls):
             return {own: tensors[part_spec.names[own]] for own in decls}
 
-        self.wte = tensors[spec.embedding.names["weight"]]
+        def make(role, part_spec):
+            cls = part_class(role, part_spec.kind)
+            return cls(part_spec, tensors_of(part_spec, cls.declare(part_spec)), self.runtime)
+
+        self.embedding = make("embedding", spec.embedding)
         self.blocks = [build_block(b, tensors_of, self.runtime) for b in spec.layers]
-        norm_cls = part_class("norm", spec.final_norm.kind)
-        self.final_norm = norm_cls(spec.final_norm, tensors_of(spec.final_norm, norm_cls.declare(spec.final_norm)),
-                                   self.runtime)
-        self.head_weight = self.wte if spec.head.tied else tensors[spec.head.names["weight"]]
-        self.head_bias = tensors[spec.head.names["bias"]] if spec.head.bias else None
+        self.final_norm = make("norm", spec.final_norm) if spec.final_norm is not None else None
+        self.head = make("head", spec.head)
+        if getattr(spec.head, "tied", False):
+            self.head.tie(self.embedding)
         self._check_schedule()
         self.n_parameters = sum(t.numel() for t in {id(t): t for t in tensors.values()}.values())
         self.weight_bytes = sum(t.numel() * t.element_size() for t in {id(t): t for t in tensors.values()}.values())
+
+    @property
+    def embedding_bytes(self) -> int:
+        """Bytes of the embedding's tensors that the head does not share: a step gathers a few rows of them."""
+        shared = {id(t) for t in vars(self.head).values() if isinstance(t, torch.Tensor)}
+        return sum(t.numel() * t.element_size() for t in vars(self.embedding).values()
+                   if isinstance(t, torch.Tensor) and id(t) not in shared)
 
     # ------------------------------------------------------------------ making a model
     @classmethod
@@ -156,7 +163,7 @@ class CausalLM:
         b = step.batch
         record = getattr(step, "nan_record", None)      # the finite check (QStream's check_nan, src/engine.c:1176-1187)
         n_runs = len(self.spec.schedule)
-        x = ops.embedding(self.wte, b.tokens, self.runtime.dtype)
+        x = self.embedding.forward(step)
         if record is not None:
             ops.check_finite(x, n_runs, record, b.tok_slot)
         for i, run in enumerate(self.spec.schedule):
@@ -166,8 +173,8 @@ class CausalLM:
         if b.n_want == 0:
             return None
         rows = ops.gather_rows(x, b.want_rows)
-        z = self.final_norm.forward(rows)
-        logits = linear(z, self.head_weight, self.head_bias, out_dtype=torch.float32)
+        z = self.final_norm.forward(rows) if self.final_norm is not None else rows
+        logits = self.head.forward(z)
         if record is not None:
             # a captured decode step wants every row, padding included: row i of the logits is row i of the step
             every_row = b.decode and b.n_want == b.n_tokens

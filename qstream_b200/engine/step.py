@@ -146,7 +146,8 @@ class Engine:
         self.graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None   # one pool: graphs never run at once
         # steps with prompts are captured too if every part goes by device metadata alone
         self.captures_prefill = self.use_graphs and all(getattr(b, "captures_any_step", False) for b in model.blocks) \
-            and getattr(model.final_norm, "captures_any_step", False)
+            and all(getattr(p, "captures_any_step", False) for p in (model.embedding, model.head)) \
+            and (model.final_norm is None or getattr(model.final_norm, "captures_any_step", False))
         self._words_host = torch.zeros(9, dtype=torch.int32).pin_memory() if self.device.type == "cuda" else None
         if verbose:
             import sys

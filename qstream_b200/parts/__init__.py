@@ -1,9 +1,9 @@
 """The parts a model is put together from, and their registries."""
-from .base import (FeedForward, Mixer, Norm, Part, PositionEncoding, Runtime, add_residuals,
+from .base import (Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, Runtime, add_residuals,
                    part_class, register)
-from . import norm, rotary, attention, mlp, block      # register the built-in kinds
+from . import norm, rotary, attention, mlp, block, embedding, head      # register the built-in kinds
 from .linear import linear
 from .block import build_block
 
-__all__ = ["FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime", "add_residuals",
+__all__ = ["Embedding", "FeedForward", "Head", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime", "add_residuals",
            "part_class", "register", "linear", "build_block"]

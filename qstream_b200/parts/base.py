@@ -15,6 +15,10 @@ mixer         kv_need() -> KvNeed | None; state_need() -> StateNeed | None;
               forward(h, step, cache_id, residuals=()) -> [T, width]
 feed_forward  forward(h, step, residuals=()) -> [T, width]
 arrangement   forward(x, step, cache_id) -> x'; built from the block's parts
+embedding     forward(step) -> x [T, width] in the activations' type, from step.batch.tokens (and, for
+              position tables, step.batch.tok_pos)
+head          forward(rows) -> float32 logits [n, vocab] of the wanted rows (already normalised by the
+              model's final norm, if it has one); `tie(embedding)` if its spec says `tied`
 
 `residuals` are tensors to be added to the part's output, in 32-bit, before the one
 rounding to the storage type; a part that cannot do that in its last kernel calls
@@ -32,7 +36,7 @@ from ..errors import QsError, QStreamError
 from ..weights.loader import TensorDecl
 
 _REGISTRY: dict[tuple[str, str], type] = {}
-ROLES = ("norm", "position", "mixer", "feed_forward", "arrangement")
+ROLES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head")
 
 
 def register(role: str, kind: str, cls: type) -> None:
@@ -110,6 +114,24 @@ class Mixer(Part):
         return None
 
     def forward(self, h, step, cache_id: int, residuals=()) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    role = "embedding"
+
+    def forward(self, step) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    role = "head"
+
+    def tie(self, embedding: "Embedding") -> None:
+        """Take the embedding's table as the weight (specs with `tied`)."""
+        raise NotImplementedError
+
+    def forward(self, rows: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 

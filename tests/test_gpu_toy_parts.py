@@ -20,7 +20,7 @@ import qstream_b200 as qs
 import plain_gptj as P
 from qstream_b200.config import (AttentionSpec, BlockSpec, EmbeddingSpec, HeadSpec, LayerRun, MlpSpec, ModelSpec,
                                  NormSpec, config_from_dict)
-from qstream_b200.parts import FeedForward, PositionEncoding, add_residuals, linear, register
+from qstream_b200.parts import Embedding, FeedForward, Head, PositionEncoding, add_residuals, linear, register
 from qstream_b200.weights import TensorDecl
 
 pytestmark = pytest.mark.gpu
@@ -265,3 +265,132 @@ def test_routed_experts_and_another_rotation(tmp_path, registered, dtype):
                     engine.release(slots[i])
             live = nxt
         engine.cache.check()
+
+
+# ----------------------------------------------------------------------------- another embedding, another head
+
+@dataclass(frozen=True)
+class PositionedEmbeddingSpec:
+    vocab_size: int
+    width: int
+    max_positions: int
+    scale: float
+    kind: str = "toy_positioned_embedding"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+class PositionedEmbedding(Embedding):
+    """x[t] = scale * table[token[t]] + positions[pos[t]]: a learned position table and an embedding scale."""
+
+    @classmethod
+    def declare(cls, spec):
+        return {"weight": TensorDecl((spec.vocab_size, spec.width)), "positions": TensorDecl((spec.max_positions, spec.width))}
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.weight, self.positions = tensors["weight"], tensors["positions"]
+
+    def forward(self, step):
+        b = step.batch
+        x = self.weight[b.tokens.long()].float() * self.spec.scale + self.positions[b.tok_pos.clamp(min=0).long()].float()
+        return x.to(self.runtime.dtype)
+
+
+@dataclass(frozen=True)
+class CappedHeadSpec:
+    vocab_size: int
+    width: int
+    cap: float
+    bias: bool = False
+    tied: bool = True
+    kind: str = "toy_capped_head"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+class CappedHead(Head):
+    """logits = cap * tanh(rows W^T / cap) with W the embedding table: a tied head with soft-capping."""
+
+    def tie(self, embedding):
+        self.weight = embedding.weight
+
+    def forward(self, rows):
+        z = linear(rows, self.weight, out_dtype=torch.float32)
+        return self.spec.cap * torch.tanh(z / self.spec.cap)
+
+
+@dataclass(frozen=True)
+class CappedToyConfig:
+    width: int
+    n_head: int
+    vocab_size: int
+    n_positions: int
+    architecture = "CappedToyForCausalLM"
+    model_type = "capped_toy"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["width"], d["n_head"], d["vocab_size"], d["n_positions"])
+
+    def to_dict(self):
+        return dict(width=self.width, n_head=self.n_head, vocab_size=self.vocab_size, n_positions=self.n_positions,
+                    architectures=[self.architecture], model_type=self.model_type)
+
+    def model_spec(self):
+        D, H = self.width, self.n_head
+        layers = tuple(
+            BlockSpec(arrangement="parallel", norms={"input": NormSpec(D, 1e-5, names={"weight": f"l{i}.n.w", "bias": f"l{i}.n.b"})},
+                      mixer=AttentionSpec(width=D, n_heads=H, n_kv_heads=H, head_dim=D // H, position=None,
+                                          names={"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "out": f"l{i}.o"}),
+                      ffn=MlpSpec(D, 2 * D, "gelu_new", names={"up": f"l{i}.up", "up_bias": f"l{i}.up_b", "down": f"l{i}.down",
+                                                               "down_bias": f"l{i}.down_b"}))
+            for i in range(2))
+        return ModelSpec(architecture=self.architecture, vocab_size=self.vocab_size, width=D, max_positions=self.n_positions,
+                         embedding=PositionedEmbeddingSpec(self.vocab_size, D, self.n_positions, 3.0,
+                                                           names={"weight": "embed", "positions": "positions"}),
+                         layers=layers, schedule=(LayerRun(0, 0), LayerRun(1, 1)),
+                         final_norm=None, head=CappedHeadSpec(self.vocab_size, D, cap=0.5))
+
+
+def plain_capped_toy(cfg, w, tokens):
+    spec = cfg.model_spec()
+    T = len(tokens)
+    x = 3.0 * w["embed"][np.asarray(tokens)] + w["positions"][:T]
+    for i, b in enumerate(spec.layers):
+        h = P.layer_norm(x, w[f"l{i}.n.w"], w[f"l{i}.n.b"], 1e-5)
+        H, dh = b.mixer.n_heads, b.mixer.head_dim
+        q, k, v = ((h @ w[f"l{i}.{n}"].T).reshape(T, H, dh) for n in "qkv")
+        a = P.causal_attention(q, k, v) @ w[f"l{i}.o"].T
+        m = P.gelu_new(h @ w[f"l{i}.up"].T + w[f"l{i}.up_b"]) @ w[f"l{i}.down"].T + w[f"l{i}.down_b"]
+        x = x + a + m
+    return 0.5 * np.tanh((x @ w["embed"].T) / 0.5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_another_embedding_and_another_head(tmp_path, dtype):
+    """The embedding and the head are registered parts like the others: a position table with an embedding scale,
+    and a tied head with soft-capping and no final norm, come from outside the library; attention runs without
+    a position part.  Whole prompts, then tokens one by one, against the plain formulas."""
+    register("embedding", "toy_positioned_embedding", PositionedEmbedding)
+    register("head", "toy_capped_head", CappedHead)
+    qs.register_architecture(CappedToyConfig, "capped_toy")
+    cfg = config_from_dict(dict(architectures=["CappedToyForCausalLM"], width=64, n_head=4, vocab_size=97, n_positions=96))
+    folder = qs.write_model_folder(tmp_path / "capped", cfg, seed=11, dtype=dtype, scales=qs.InitScales(0.05, 0.1, 0.02))
+    w = P.read_safetensors(folder / "model.safetensors")
+    assert set(w) >= {"embed", "positions"} and "head.w" not in w
+    model = qs.load_model(folder, dtype=dtype, device="cuda")
+    engine = qs.Engine(model, max_tokens=64 * 4, max_batch=2)
+    assert not engine.captures_prefill                  # the toy parts do not claim to go by device metadata alone
+    rng = np.random.default_rng(3)
+    reqs = [[int(t) for t in rng.integers(0, 97, n)] for n in (70, 9)]
+    atol = 2e-4 if dtype == "float32" else 2e-2
+    slots = [engine.acquire(), engine.acquire()]
+    heads = [60, 4]
+    out = engine.step(slots, [r[:h] for r, h in zip(reqs, heads)], [list(range(h)) for h in heads]).cpu().double().numpy()
+    np.testing.assert_allclose(out[:60], plain_capped_toy(cfg, w, reqs[0])[:60], atol=atol)
+    np.testing.assert_allclose(out[60:], plain_capped_toy(cfg, w, reqs[1])[:4], atol=atol)
+    assert np.abs(out).max() <= 0.5 + 1e-6 and np.abs(out).max() > 0.05
+    for step in range(5):                                # both decode on: a captured decode step with the toy parts
+        out = engine.step(slots, [[r[h + step]] for r, h in zip(reqs, heads)]).cpu().double().numpy()
+        for i, (r, h) in enumerate(zip(reqs, heads)):
+            np.testing.assert_allclose(out[i], plain_capped_toy(cfg, w, r)[h + step], atol=atol)
+    engine.check_status()
