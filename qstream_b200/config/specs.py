@@ -91,9 +91,10 @@ class BlockSpec:
 class LayerRun:
     """One entry of the schedule: run layer `layer` against cache entry `cache`.
     A layer may appear in several runs; two runs may name the same cache entry
-    when the later one only reads it."""
+    when the later one only reads it.  For a layer with several parts that use the
+    cache, `cache` is a tuple with one entry id per such part."""
     layer: int
-    cache: int
+    cache: object
 
 
 @dataclass(frozen=True)
@@ -131,4 +132,5 @@ class ModelSpec:
     bos_token_id: Optional[int] = None
 
     def n_cache_entries(self) -> int:
-        return 1 + max((r.cache for r in self.schedule), default=-1)
+        ids = [c for r in self.schedule for c in (r.cache if isinstance(r.cache, (tuple, list)) else (r.cache,))]
+        return 1 + max(ids, default=-1)

@@ -38,8 +38,7 @@ def _part_declarations(spec: ModelSpec):
     """Yield (part spec, {own name: TensorDecl}) for every part that holds tensors."""
     yield spec.embedding, part_class("embedding", spec.embedding.kind).declare(spec.embedding)
     for block in spec.layers:
-        for role, ps in (("mixer", block.mixer), ("feed_forward", block.ffn),
-                         *(("norm", n) for n in block.norms.values())):
+        for role, ps in part_class("arrangement", block.arrangement).part_specs(block):
             yield ps, part_class(role, ps.kind).declare(ps)
     if spec.final_norm is not None:
         yield spec.final_norm, part_class("norm", spec.final_norm.kind).declare(spec.final_norm)
@@ -122,39 +121,38 @@ class CausalLM:
         return cls(spec, tensors, dtype, device, config)
 
     # ------------------------------------------------------------------ what the cache must hold
-    def _check_schedule(self):
-        writers = {}
+    def _cache_users(self):
+        """Yield (schedule index, cache entry id, part) for every part of every run that uses the cache."""
         for i, run in enumerate(self.spec.schedule):
             if not 0 <= run.layer < len(self.blocks):
                 raise QStreamError(QsError.INVALID_MODEL, f"schedule entry {i} names layer {run.layer}")
-            mixer = self.blocks[run.layer].mixer
-            if mixer.kv_need() is not None or mixer.state_need() is not None:
-                if run.cache in writers:
+            parts = self.blocks[run.layer].cached_parts()
+            ids = run.cache if isinstance(run.cache, (tuple, list)) else (run.cache,)
+            if len(ids) != len(parts):
+                raise QStreamError(QsError.INVALID_MODEL,
+                                   f"schedule entry {i} names {len(ids)} cache entries, layer {run.layer} has "
+                                   f"{len(parts)} parts that use the cache")
+            yield from ((i, cid, part) for cid, part in zip(ids, parts))
+
+    def _check_schedule(self):
+        writers = {}
+        for i, cid, part in self._cache_users():
+            if part.kv_need() is not None or part.state_need() is not None:
+                if cid in writers:
                     raise QStreamError(QsError.INVALID_MODEL,
-                                       f"schedule entries {writers[run.cache]} and {i} both write cache entry {run.cache}")
-                writers[run.cache] = i
-        for i, run in enumerate(self.spec.schedule):
-            spec = self.blocks[run.layer].mixer.spec
-            if getattr(spec, "shares_cache", False):
-                if run.cache not in writers or writers[run.cache] > i:
+                                       f"schedule entries {writers[cid]} and {i} both write cache entry {cid}")
+                writers[cid] = i
+        for i, cid, part in self._cache_users():
+            if getattr(part.spec, "shares_cache", False):
+                if cid not in writers or writers[cid] > i:
                     raise QStreamError(QsError.INVALID_MODEL,
-                                       f"schedule entry {i} reads cache entry {run.cache} before any layer wrote it")
+                                       f"schedule entry {i} reads cache entry {cid} before any layer wrote it")
 
     def kv_needs(self) -> dict[int, KvNeed]:
-        out = {}
-        for run in self.spec.schedule:
-            need = self.blocks[run.layer].mixer.kv_need()
-            if need is not None:
-                out[run.cache] = need
-        return out
+        return {cid: part.kv_need() for _, cid, part in self._cache_users() if part.kv_need() is not None}
 
     def state_needs(self) -> dict[int, StateNeed]:
-        out = {}
-        for run in self.spec.schedule:
-            need = self.blocks[run.layer].mixer.state_need()
-            if need is not None:
-                out[run.cache] = need
-        return out
+        return {cid: part.state_need() for _, cid, part in self._cache_users() if part.state_need() is not None}
 
     # ------------------------------------------------------------------ forward
     def forward(self, step) -> torch.Tensor | None:

@@ -24,7 +24,8 @@ class Arrangement(Part):
         self.norms = parts["norms"]
         position = getattr(self.mixer, "position", None)
         self.captures_any_step = self.captures_own_step and all(
-            p.captures_any_step for p in (self.mixer, self.ffn, *self.norms.values(), *([position] if position else [])))
+            getattr(p, "captures_any_step", False)
+            for p in (self.mixer, self.ffn, *self.norms.values(), *([position] if position else [])))
         missing = [n for n in self.norm_names if n not in self.norms]
         if missing:
             raise QStreamError(QsError.INVALID_MODEL,
@@ -33,6 +34,30 @@ class Arrangement(Part):
 
     def forward(self, x, step, cache_id):
         raise NotImplementedError
+
+    # What a layer is made of is the arrangement's own business.  The three methods below describe the layers
+    # of this library (one mixer, one feed-forward, named norms); an arrangement of another make - two mixers,
+    # no feed-forward - overrides them and nothing else in the library changes.
+    @classmethod
+    def part_specs(cls, spec):
+        """Yield (role, part spec) for every part of the layer that holds tensors."""
+        yield "mixer", spec.mixer
+        yield "feed_forward", spec.ffn
+        for norm_spec in spec.norms.values():
+            yield "norm", norm_spec
+
+    @classmethod
+    def build(cls, spec, make, runtime):
+        """Build the layer; `make(role, part_spec)` builds one part with its tensors."""
+        parts = {"mixer": make("mixer", spec.mixer), "ffn": make("feed_forward", spec.ffn),
+                 "norms": {name: make("norm", ns) for name, ns in spec.norms.items()}}
+        return cls(spec, parts, runtime)
+
+    def cached_parts(self):
+        """The parts that keep something in the cache (keys and values, or state), in the order of the
+        cache entries a schedule run names for this layer: `LayerRun.cache` is one id for one such part, a
+        tuple of ids for several; `forward` gets it as it stands."""
+        return [self.mixer]
 
 
 SIDE_STREAM_MAX_TOKENS = 2
@@ -106,9 +131,4 @@ def build_block(spec, tensors_of, runtime):
         cls = part_class(role, part_spec.kind)
         return cls(part_spec, tensors_of(part_spec, cls.declare(part_spec)), runtime)
 
-    parts = {
-        "mixer": make("mixer", spec.mixer),
-        "ffn": make("feed_forward", spec.ffn),
-        "norms": {name: make("norm", ns) for name, ns in spec.norms.items()},
-    }
-    return part_class("arrangement", spec.arrangement)(spec, parts, runtime)
+    return part_class("arrangement", spec.arrangement).build(spec, make, runtime)

@@ -18,7 +18,8 @@ from qstream_b200.cache import StateNeed
 from qstream_b200.config import (AttentionSpec, BlockSpec, EmbeddingSpec, HeadSpec, LayerRun, MlpSpec, ModelSpec,
                                  NormSpec, PositionSpec, config_from_dict)
 from qstream_b200.engine.model import declared_tensors
-from qstream_b200.parts import Mixer, add_residuals, linear, register
+from qstream_b200.parts import Mixer, Part, add_residuals, linear, register
+from qstream_b200.parts.block import Arrangement
 from qstream_b200.weights import TensorDecl
 
 pytestmark = pytest.mark.gpu
@@ -230,3 +231,123 @@ def test_schedule_errors(registered):
         tensors = random_tensors(declared_tensors(spec), 0, torch.float32, "cuda")
         with pytest.raises(qs.QStreamError, match=what):
             qs.CausalLM(spec, tensors, "float32", "cuda")
+
+
+# ----------------------------------------------------------------------------- a layer of another make
+
+@dataclass(frozen=True)
+class TwoMixerBlockSpec:
+    """x + attention(norm x) + running_mean(norm x): two mixers that both use the cache, no feed-forward."""
+    attention: object
+    mean: object
+    norm: object
+    arrangement: str = "toy_two_mixers"
+
+
+class TwoMixerBlock(Arrangement):
+    @classmethod
+    def part_specs(cls, spec):
+        yield "mixer", spec.attention
+        yield "mixer", spec.mean
+        yield "norm", spec.norm
+
+    @classmethod
+    def build(cls, spec, make, runtime):
+        self = cls.__new__(cls)
+        Part.__init__(self, spec, {}, runtime)
+        self.attention, self.mean, self.norm = make("mixer", spec.attention), make("mixer", spec.mean), make("norm", spec.norm)
+        return self
+
+    def cached_parts(self):
+        return [self.attention, self.mean]
+
+    def forward(self, x, step, cache_id):
+        keys, state = cache_id                              # one cache entry per part that uses the cache
+        h = self.norm.forward(x)
+        a = self.attention.forward(h, step, keys)
+        return self.mean.forward(h, step, state, residuals=(x, a))
+
+
+@dataclass(frozen=True)
+class TwoMixerConfig:
+    width: int
+    n_head: int
+    vocab_size: int
+    n_positions: int
+    architecture = "TwoMixerForCausalLM"
+    model_type = "two_mixer_toy"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["width"], d["n_head"], d["vocab_size"], d["n_positions"])
+
+    def to_dict(self):
+        return dict(width=self.width, n_head=self.n_head, vocab_size=self.vocab_size, n_positions=self.n_positions,
+                    architectures=[self.architecture], model_type=self.model_type)
+
+    def model_spec(self):
+        D, H = self.width, self.n_head
+        pos = PositionSpec(rotary_dim=D // H // 2, base=10000.0, max_positions=self.n_positions)
+        layers = tuple(TwoMixerBlockSpec(
+            attention=AttentionSpec(width=D, n_heads=H, n_kv_heads=H, head_dim=D // H, position=pos,
+                                    names={"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "out": f"l{i}.o"}),
+            mean=RunningMeanSpec(width=D, names={"proj": f"l{i}.mean"}),
+            norm=NormSpec(D, 1e-5, names={"weight": f"l{i}.n.w", "bias": f"l{i}.n.b"})) for i in range(2))
+        return ModelSpec(architecture=self.architecture, vocab_size=self.vocab_size, width=D, max_positions=self.n_positions,
+                         embedding=EmbeddingSpec(self.vocab_size, D, names={"weight": "embed"}), layers=layers,
+                         schedule=(LayerRun(0, (0, 1)), LayerRun(1, (2, 3))),
+                         final_norm=NormSpec(D, 1e-5, names={"weight": "norm.w", "bias": "norm.b"}),
+                         head=HeadSpec(self.vocab_size, D, bias=False, tied=True, names={}))
+
+
+def plain_two_mixers(cfg, w, tokens):
+    T = len(tokens)
+    posn = np.arange(T)
+    H, dh = cfg.n_head, cfg.width // cfg.n_head
+    x = w["embed"][np.asarray(tokens)]
+    for i in range(2):
+        h = P.layer_norm(x, w[f"l{i}.n.w"], w[f"l{i}.n.b"], 1e-5)
+        q = P.rotary_interleaved((h @ w[f"l{i}.q"].T).reshape(T, H, dh), posn, dh // 2)
+        k = P.rotary_interleaved((h @ w[f"l{i}.k"].T).reshape(T, H, dh), posn, dh // 2)
+        v = (h @ w[f"l{i}.v"].T).reshape(T, H, dh)
+        a = P.causal_attention(q, k, v) @ w[f"l{i}.o"].T
+        m = (np.cumsum(h, 0) / (posn[:, None] + 1.0)) @ w[f"l{i}.mean"].T
+        x = x + a + m
+    return P.layer_norm(x, w["norm.w"], w["norm.b"], 1e-5) @ w["embed"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layer_with_two_mixers_and_no_feed_forward(tmp_path, registered, dtype):
+    """What a layer is made of belongs to its arrangement: one registered here has two mixers that both use
+    the cache (keys and values; a running sum) and no feed-forward, and each schedule run names two cache
+    entries.  Nothing of the library changes."""
+    register("arrangement", "toy_two_mixers", TwoMixerBlock)
+    qs.register_architecture(TwoMixerConfig, "two_mixer_toy")
+    cfg = config_from_dict(dict(architectures=["TwoMixerForCausalLM"], width=64, n_head=2, vocab_size=83, n_positions=128))
+    folder = qs.write_model_folder(tmp_path / "two", cfg, seed=6, dtype=dtype)
+    model = qs.load_model(folder, dtype=dtype, device="cuda")
+    assert set(model.kv_needs()) == {0, 2} and set(model.state_needs()) == {1, 3}
+    engine = qs.Engine(model, max_tokens=64 * 4, max_batch=2)
+    w = P.read_safetensors(folder / "model.safetensors")
+    rng = np.random.default_rng(7)
+    reqs = [[int(t) for t in rng.integers(0, 83, n)] for n in (80, 21)]
+    refs = [plain_two_mixers(cfg, w, r) for r in reqs]
+    atol = 2e-4 if dtype == "float32" else 6e-2
+    for _ in range(2):                                      # twice: slots, pages and state are used again
+        slots = [engine.acquire(), engine.acquire()]
+        heads = [66, 5]
+        out = engine.step(slots, [r[:h] for r, h in zip(reqs, heads)], [list(range(h)) for h in heads]).cpu().double().numpy()
+        np.testing.assert_allclose(out[:66], refs[0][:66], atol=atol, rtol=5e-2)
+        np.testing.assert_allclose(out[66:], refs[1][:5], atol=atol, rtol=5e-2)
+        for step in range(10):
+            out = engine.step(slots, [[r[h + step]] for r, h in zip(reqs, heads)]).cpu().double().numpy()
+            for i, (r, h) in enumerate(zip(reqs, heads)):
+                np.testing.assert_allclose(out[i], refs[i][h + step], atol=atol, rtol=5e-2)
+        for s in slots:
+            engine.release(s)
+        engine.cache.check()
+    with pytest.raises(qs.QStreamError, match="cache entries"):
+        import dataclasses
+        from qstream_b200.weights import random_tensors
+        spec = dataclasses.replace(cfg.model_spec(), schedule=(LayerRun(0, 0), LayerRun(1, (2, 3))))
+        qs.CausalLM(spec, random_tensors(declared_tensors(spec), 0, torch.float32, "cuda"), "float32", "cuda")
