@@ -321,3 +321,76 @@ def test_captured_steps_with_prompts(tmp_path, which, dtype):
     a = [eng.acquire(), eng.acquire()]
     b = [plain_eng.acquire(), plain_eng.acquire()]
     assert torch.equal(eng.step(a, toks), plain_eng.step(b, toks))
+
+
+@pytest.mark.parametrize("which,dtype,seed", [("A", "float32", 0), ("B", "bfloat16", 1), ("A", "bfloat16", 2), ("B", "float32", 3)])
+def test_random_walk_of_steps(tmp_path, which, dtype, seed):
+    """Some three hundred steps drawn at random: sequences start and end at any time, a step brings any mix
+    of prompt chunks, single tokens and idle sequences, wants the last place, every place or none, and slots
+    and pages change hands all the while.  Every logits row that comes back is compared with the plain model
+    on that sequence's tokens so far."""
+    folder, cfg = make_folder(tmp_path, which, dtype)
+    eng = engine_for(folder, dtype, max_tokens=64 * 14, max_batch=6)
+    rng = np.random.default_rng(100 + seed)
+    limit = cfg.n_positions
+    live = {}                                           # slot -> (all tokens of the request, tokens fed so far)
+    plain_cache = {}
+    checked = 0
+
+    def reference(tokens, upto):
+        key = tuple(tokens)
+        if key not in plain_cache:
+            plain_cache[key] = plain_logits(folder, tokens)
+        return plain_cache[key][:upto]
+
+    for step_no in range(300):
+        # sequences come ...
+        while len(live) < 6 and (not live or rng.random() < 0.3):
+            n = int(rng.integers(1, limit + 1)) if rng.random() < 0.2 else int(rng.integers(1, 70))
+            try:
+                live[eng.acquire()] = (random_tokens(rng, n, cfg.vocab_size), 0)
+            except qs.QStreamError:
+                break
+        # ... a step for a random subset, each with a random number of its next tokens (0: idle)
+        chosen = [s for s in live if rng.random() < 0.8] or list(live)
+        kind = rng.random()
+        tokens, want = [], []
+        for s in chosen:
+            toks, fed = live[s]
+            left = len(toks) - fed
+            n = min(left, 1 if kind < 0.45 else int(rng.integers(0, 40)))
+            tokens.append(toks[fed:fed + n])
+            w = rng.random()
+            want.append(([n - 1] if n else []) if w < 0.5 else (list(range(n)) if w < 0.85 else []))
+        try:
+            out = eng.step(chosen, tokens, None if all(w == ([len(t) - 1] if t else []) for w, t in zip(want, tokens)) and all(tokens) else want)
+        except qs.QStreamError as e:                    # the cache is full: end the longest sequence and go on
+            assert e.code == qs.QsError.BUDGET_EXCEEDED, e
+            victim = max(live, key=lambda s: live[s][1])
+            eng.release(victim)
+            del live[victim]
+            continue
+        rows = out.cpu().numpy() if out is not None else np.zeros((0, cfg.vocab_size))
+        row = 0
+        for s, t, w in zip(chosen, tokens, want):
+            toks, fed = live[s]
+            for place in w:
+                ref = reference(toks, fed + place + 1)[-1]
+                assert_logits_close(rows[row:row + 1], ref[None], dtype, f"step {step_no} slot {s} position {fed + place}")
+                row += 1
+                checked += 1
+            live[s] = (toks, fed + len(t))
+        assert row == rows.shape[0]
+        # ... and go: when all their tokens are in, or at random
+        for s in list(live):
+            toks, fed = live[s]
+            if fed == len(toks) or rng.random() < 0.03:
+                eng.release(s)
+                del live[s]
+        if step_no % 50 == 49:
+            eng.check_status()
+            eng.cache.check()
+    eng.check_status()
+    eng.cache.check()
+    eng.cache.check_canaries()
+    assert checked > 300
