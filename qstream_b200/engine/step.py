@@ -186,13 +186,8 @@ class Engine:
         """Check the step, hand out its cache pages and upload its metadata."""
         if len(slots) != len(tokens) or (want is not None and len(want) != len(slots)):
             raise QStreamError(QsError.INVALID_INPUT, "step: slots, tokens and want differ in length")
-        V = self.model.vocab_size
         n_new = [len(t) for t in tokens]
-        for s, toks in zip(slots, tokens):
-            for tok in toks:
-                if not 0 <= int(tok) < V:
-                    raise QStreamError(QsError.INVALID_INPUT,
-                                       f"token id {tok} (slot {s}) outside the vocabulary of {V}")
+        tokens = self._checked_tokens(slots, tokens)
         if want is None:
             want = [[n - 1] if n else [] for n in n_new]
         for w, n in zip(want, n_new):
@@ -233,6 +228,22 @@ class Engine:
             want_rows=views[3], seq_slot=views[4], seq_start=views[5], seq_p0=views[6],
             slots=list(slots), new_tokens=n_new, p0=p0, decode=bool(n_new) and all(n == 1 for n in n_new),
             max_new=max(n_new, default=0), max_total=max((a + b for a, b in zip(p0, n_new)), default=0))
+
+    def _checked_tokens(self, slots, tokens) -> list:
+        """Each sequence's tokens as an int64 array, every id inside the vocabulary (checked in one pass each:
+        a prompt of thousands of tokens is not walked in Python)."""
+        V = self.model.vocab_size
+        out = []
+        for s, toks in zip(slots, tokens):
+            try:
+                a = np.asarray(toks, dtype=np.int64).reshape(-1)
+            except (TypeError, ValueError, OverflowError):
+                raise QStreamError(QsError.INVALID_INPUT, f"the tokens of slot {s} are not integers") from None
+            if a.size and (int(a.min()) < 0 or int(a.max()) >= V):
+                bad = int(a[(a < 0) | (a >= V)][0])
+                raise QStreamError(QsError.INVALID_INPUT, f"token id {bad} (slot {s}) outside the vocabulary of {V}")
+            out.append(a)
+        return out
 
     def _upload(self, host: np.ndarray) -> torch.Tensor:
         t = torch.from_numpy(host)
@@ -288,12 +299,7 @@ class Engine:
         size = prefill_bucket(sum(n_new), len(slots))
         if size is None:
             return None
-        V = self.model.vocab_size
-        for s, toks in zip(slots, tokens):
-            for tok in toks:
-                if not 0 <= int(tok) < V:
-                    raise QStreamError(QsError.INVALID_INPUT,
-                                       f"token id {tok} (slot {s}) outside the vocabulary of {V}")
+        tokens = self._checked_tokens(slots, tokens)
         self.cache.prepare(slots, n_new)
         p0 = [self.cache.length(s) for s in slots]
         graph = self._prefill_graphs.get(size)
