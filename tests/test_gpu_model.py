@@ -394,3 +394,36 @@ def test_random_walk_of_steps(tmp_path, which, dtype, seed):
     eng.cache.check()
     eng.cache.check_canaries()
     assert checked > 300
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_odd_engine_sizes(tmp_path, dtype):
+    """A context that is no multiple of a page or of a split, and more sequences than any usual batch: seventy
+    sequences decode together (a captured step of 96 rows), each against the plain model."""
+    folder, cfg = make_folder(tmp_path, "B", dtype)
+    model = qs.load_model(folder, dtype=dtype, device="cuda")
+    eng = qs.Engine(model, max_tokens=70 * 128, max_batch=70, max_context=100)
+    rng = np.random.default_rng(19)
+    lens = [int(rng.integers(1, 60)) for _ in range(70)]
+    reqs = [random_tokens(rng, n + 3, cfg.vocab_size) for n in lens]
+    slots = [eng.acquire() for _ in reqs]
+    out = [eng.step(slots[a:a + 10], [r[:n] for r, n in zip(reqs[a:a + 10], lens[a:a + 10])]).cpu().numpy()
+           for a in range(0, 70, 10)]
+    got = [[row[None]] for chunk in out for row in chunk]
+    for k in range(3):
+        step = eng.step(slots, [[r[n + k]] for r, n in zip(reqs, lens)]).cpu().numpy()
+        for i in range(70):
+            got[i].append(step[i:i + 1])
+    eng.check_status()
+    for i in (0, 7, 33, 69):
+        ref = plain_logits(folder, reqs[i])[lens[i] - 1:]
+        assert_logits_close(np.concatenate(got[i]), ref, dtype, f"{dtype} request {i} of 70")
+    # the context of 100 is the limit, whatever the pages could hold
+    s = slots[0]
+    eng.step([s], [random_tokens(rng, 100 - eng.length(s), cfg.vocab_size)])
+    with pytest.raises(qs.QStreamError) as e:
+        eng.step([s], [[1]])
+    assert e.value.code == qs.QsError.SEQ_TOO_LONG
+    for s in slots:
+        eng.release(s)
+    eng.cache.check()
