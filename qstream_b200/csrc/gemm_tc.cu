@@ -800,7 +800,7 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
 }
 
 template <int BN>
-int launch_stream(const void* W, const CUtensorMap& ma, const Epilogue& ep, int N, int K, float* ws,
+int launch_stream(const void* W, long long ldw, const CUtensorMap& ma, const Epilogue& ep, int N, int K, float* ws,
                   long long ws_floats, int32_t* counters, int n_counters, int32_t* status, cudaStream_t stream) {
     static bool configured = false;
     static int sm_count = 0;
@@ -840,7 +840,7 @@ int launch_stream(const void* W, const CUtensorMap& ma, const Epilogue& ep, int 
     if (stages > MAX_STREAM_STAGES) stages = MAX_STREAM_STAGES;
     const int smem = 2048 + stages * stage + STREAM_PAD;
     CUtensorMap mw;
-    int rc = tensor_map(&mw, W, N, K, K, (int)rows);
+    int rc = tensor_map(&mw, W, N, K, ldw, (int)rows);
     if (rc != QS_OK) return rc;
     cudaError_t e = qs_launch_dependent(gemm_tc_stream_kernel<BN>, dim3((unsigned)G), dim3(THREADS), (size_t)smem, stream,
                                         mw, ma, ep, K, (int)tiles, (int)rows, stages, ws, counters, status);
@@ -887,11 +887,11 @@ int pair_max_clusters() {
 }
 
 template <int PAIR_BN>
-int launch_pair(const CUtensorMap& ma, const void* W, const Epilogue& ep, int M, int N, int K, float* ws,
+int launch_pair(const CUtensorMap& ma, const void* W, long long ldw, const Epilogue& ep, int M, int N, int K, float* ws,
                 long long ws_floats, int32_t* counters, int n_counters, int32_t* status, cudaStream_t stream) {
     const int max_clusters = pair_max_clusters<PAIR_BN>();
     CUtensorMap mw;
-    int rc = tensor_map(&mw, W, N, K, K, PAIR_BN / 2);
+    int rc = tensor_map(&mw, W, N, K, ldw, PAIR_BN / 2);
     if (rc != QS_OK) return rc;
     const int m_pairs = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + PAIR_BN - 1) / PAIR_BN;
     const long long tiles = (long long)m_pairs * n_tiles;
@@ -934,19 +934,21 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const Epilog
 
 }  // namespace
 
-// A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16 contiguous; C: [M, N] bfloat16 or float32.
+// A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16, row stride ldw (a matrix, or columns of a wider
+// one); C: [M, N] bfloat16 or float32.
 // res1/res2: bfloat16 [M, N] with row stride ldr, or null.  status: device int32 that receives a
 // non-zero code if a bounded wait inside the kernel ran out.
 // ws / counters: scratch for split-K in the weight-streaming arrangement (M <= 128): `ws_floats` floats
 // and `n_counters` int32 that are ZERO before the first call (the kernel leaves them zero).  Without
 // them (null) the product runs unsplit.  Calls that share the scratch must not overlap on the GPU.
 QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const void* bias, int bias_dtype, int act,
-                      const void* res1, const void* res2, int M, int N, int K, long long lda, long long ldc,
-                      long long ldr, float* ws, long long ws_floats, int32_t* counters, int n_counters,
+                      const void* res1, const void* res2, int M, int N, int K, long long lda, long long ldw,
+                      long long ldc, long long ldr, float* ws, long long ws_floats, int32_t* counters, int n_counters,
                       int32_t* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return QS_OK;
     QS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
-    QS_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc: K=%d and the row stride %lld must be multiples of 8", K, lda);
+    QS_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ldw >= K,
+               "gemm_tc: K=%d and the row strides %lld, %lld must be multiples of 8, the matrix's at least K", K, lda, ldw);
     QS_REQUIRE(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0, "gemm_tc: operands must be 16-byte aligned");
     QS_REQUIRE(c_dtype == QS_F32 || c_dtype == QS_BF16, "gemm_tc: unknown output type %d", c_dtype);
     Epilogue ep{C, c_dtype, ldc, bias, bias_dtype, act, (const __nv_bfloat16*)res1, (const __nv_bfloat16*)res2, ldr, M, N};
@@ -971,19 +973,19 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
                 const long long r256 = cost(256, c256);
                 const long long r192 = c192 > 0 ? cost(192, c192) : r256;
                 if (r192 * 112 < r256 * 100)
-                    return launch_pair<192>(ma, W, ep, M, N, K, ws, ws_floats, counters, n_counters, status, stream);
-                return launch_pair<256>(ma, W, ep, M, N, K, ws, ws_floats, counters, n_counters, status, stream);
+                    return launch_pair<192>(ma, W, ldw, ep, M, N, K, ws, ws_floats, counters, n_counters, status, stream);
+                return launch_pair<256>(ma, W, ldw, ep, M, N, K, ws, ws_floats, counters, n_counters, status, stream);
             }
         }
         const int bn = N > 128 ? 256 : 128;
-        if ((rc = tensor_map(&mw, W, N, K, K, bn)) != QS_OK) return rc;
+        if ((rc = tensor_map(&mw, W, N, K, ldw, bn)) != QS_OK) return rc;
         if (bn == 256) return launch_persistent<256>(ma, mw, ep, M, N, K, status, stream);
         return launch_persistent<128>(ma, mw, ep, M, N, K, status, stream);
     }
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     if ((rc = tensor_map(&ma, A, M, K, lda, bn)) != QS_OK) return rc;
-    if (bn == 16) return launch_stream<16>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    if (bn == 32) return launch_stream<32>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    if (bn == 64) return launch_stream<64>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    return launch_stream<128>(W, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    if (bn == 16) return launch_stream<16>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    if (bn == 32) return launch_stream<32>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    if (bn == 64) return launch_stream<64>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    return launch_stream<128>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
 }

@@ -17,7 +17,7 @@ def _entry():
     if _fn is None:
         _fn = ops.bind("qs_gemm_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                                      c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
+                                      c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
     return _fn
 
 
@@ -67,9 +67,11 @@ def check_status(device) -> None:
 
 
 def takes(x, weight) -> bool:
-    """Whether the tensor-core kernel takes these operands: bfloat16, rows of 16-byte pitch."""
+    """Whether the tensor-core kernel takes these operands: bfloat16, rows of 16-byte pitch (the matrix may
+    be a range of columns of a wider one)."""
     return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
-            and weight.is_contiguous() and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and weight.dim() == 2 and weight.stride(1) == 1 and weight.stride(0) % 8 == 0
+            and weight.stride(0) >= weight.shape[1] and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
@@ -96,7 +98,7 @@ def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, 
     ws, counters = scratch(x.device)
     ops.check(_entry()(ops.ptr(out), ops.dtype_code(out), ops.ptr(x), ops.ptr(weight), ops.ptr(bias),
                        ops.dtype_code(bias) if bias is not None else 0, ops.ACTIVATIONS[activation],
-                       ops.ptr(res[0]), ops.ptr(res[1]), M, N, K, x.stride(0), out.stride(0), ldr,
+                       ops.ptr(res[0]), ops.ptr(res[1]), M, N, K, x.stride(0), weight.stride(0), out.stride(0), ldr,
                        ops.ptr(ws), ws.numel(), ops.ptr(counters), counters.numel(),
                        ops.ptr(status_word(x.device)), ops.stream()))
     return out

@@ -15,7 +15,9 @@ from .base import Part, part_class, register
 class Arrangement(Part):
     role = "arrangement"
     norm_names: tuple = ()
-    captures_own_step = True            # the arrangements here read nothing of the step but `decode`
+    # the arrangements here read nothing of the step but `decode` and, of a decode step, the number of rows
+    # and the longest sequence (which a captured decode step is keyed by)
+    captures_own_step = True
 
     def __init__(self, spec, parts, runtime):
         super().__init__(spec, {}, runtime)
@@ -60,14 +62,21 @@ class Arrangement(Part):
         return [self.mixer]
 
 
-SIDE_STREAM_MAX_TOKENS = 2
+# A decode step whose rows together hold at most this many keys (rows x the longest sequence) runs its
+# two branches side by side; beyond it the attention kernels are bound by memory like the products.
+SIDE_BRANCH_MAX_KEYS = 4096
 
 
 class ParallelBlock(Arrangement):
     """x + mixer(h) + ffn(h).  When both parts end in a projection to the width (they offer
     `output_projection()` and `forward_hidden(..., out=view)`) and the weights are bfloat16, the two
     projections become one matrix product over the concatenated hidden vectors:
-    x + [o | g] [W_o | W_down]^T + (b_o + b_down), with the residual added on its 32-bit accumulator."""
+    x + [o | g] [W_o | W_down]^T + (b_o + b_down), with the residual added on its 32-bit accumulator.
+
+    Decode steps over few keys are bound by the latency of the attention kernels, not by memory: there the
+    feed-forward runs whole on a second stream beside the mixer (its two products stream their weights
+    while the attention kernels wait for theirs), and the mixer's output product - over its columns of
+    the fused matrix - adds x and the feed-forward's result on its 32-bit accumulator."""
     norm_names = ("input",)
 
     def __init__(self, spec, parts, runtime):
@@ -94,21 +103,21 @@ class ParallelBlock(Arrangement):
             return self.ffn.forward(h, step, residuals=(x, a))
         import torch
         from .linear import linear
-        hidden = torch.empty((h.shape[0], self.fused_weight.shape[1]), dtype=h.dtype, device=h.device)
+        b = step.batch
         side = getattr(step, "side_stream", None)
-        if side is not None and step.batch.decode and h.shape[0] <= SIDE_STREAM_MAX_TOKENS:
-            # One or two tokens: the attention kernels are short and mostly latency, and the feed-forward's
-            # first product needs only h, so it runs on a second stream beside them (7 % and 5 % more tokens
-            # a second at batch 1 and 2).  From four tokens on the product would hold every SM's shared
-            # memory while the attention kernels want to start, and the step gets slower.
+        if side is not None and b.decode and h.shape[0] * (b.max_total or step.cache.max_context) <= SIDE_BRANCH_MAX_KEYS:
+            # Measured on a B200 at GPT-J-6B's sizes against the one fused product: 7 to 13 % more tokens a
+            # second up to 4,096 keys (1 x 2,048, 4 x 1,024, 8 x 512, 16 x 256), 3 to 5 % fewer from 8,192 on.
             from .linear import beside_main_stream
             with beside_main_stream(side, h.device) as beside:
-                self.ffn.forward_hidden(h, step, out=hidden[:, self.k_mixer:])
-            self.mixer.forward_hidden(h, step, cache_id, out=hidden[:, :self.k_mixer])
+                g = self.ffn.forward_hidden(h, step)
+                m = linear(g, self.fused_weight[:, self.k_mixer:], self.fused_bias)
+            o = self.mixer.forward_hidden(h, step, cache_id)
             beside.join()
-        else:
-            self.mixer.forward_hidden(h, step, cache_id, out=hidden[:, :self.k_mixer])
-            self.ffn.forward_hidden(h, step, out=hidden[:, self.k_mixer:])
+            return linear(o, self.fused_weight[:, :self.k_mixer], None, residuals=(x, m))
+        hidden = torch.empty((h.shape[0], self.fused_weight.shape[1]), dtype=h.dtype, device=h.device)
+        self.mixer.forward_hidden(h, step, cache_id, out=hidden[:, :self.k_mixer])
+        self.ffn.forward_hidden(h, step, out=hidden[:, self.k_mixer:])
         return linear(hidden, self.fused_weight, self.fused_bias, residuals=(x,))
 
 

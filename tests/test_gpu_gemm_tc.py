@@ -122,3 +122,25 @@ def test_cta_pairs_cut_along_k(M, N, K):
     plain = gemm_tc.linear(x, w, out_dtype=torch.float32)
     np.testing.assert_allclose(f64(plain), f64(x) @ f64(w).T, atol=2e-3, rtol=2e-3)
     gemm_tc.check_status(x.device)
+
+
+@pytest.mark.parametrize("M", [1, 8, 64, 100, 300, 1000])
+def test_matrix_as_columns_of_a_wider_one(M):
+    """The matrix may be a range of columns of a wider one (row stride beyond K), as the two halves of a
+    block's fused output matrix are: the same bits as with a copy of those columns, in every arrangement
+    of the kernel (weights streamed, tiles, CTA pairs)."""
+    g = torch.Generator().manual_seed(M)
+    wide = (torch.randn(520, 1024 + 2048, generator=g) / 40).bfloat16().cuda()
+    bias = torch.randn(520, generator=g).float().cuda()
+    for lo, hi in ((0, 1024), (1024, 3072), (8, 3064)):
+        x = torch.randn(M, hi - lo, generator=g).bfloat16().cuda()
+        res = torch.randn(M, 520, generator=g).bfloat16().cuda()
+        view = wide[:, lo:hi]
+        assert not view.is_contiguous() and gemm_tc.takes(x, view)
+        got = gemm_tc.linear(x, view, bias, "gelu", (res,), torch.float32)
+        assert torch.equal(got, gemm_tc.linear(x, view.contiguous(), bias, "gelu", (res,), torch.float32))
+        ref = P.gelu_erf(f64(x) @ f64(view).T + f64(bias)) + f64(res)
+        np.testing.assert_allclose(f64(got), ref, atol=3e-3, rtol=3e-3)
+    assert not gemm_tc.takes(x, wide[:, 4:1028])          # a view that starts off a 16-byte boundary
+    assert not gemm_tc.takes(x, wide.T)
+    gemm_tc.check_status(x.device)

@@ -427,3 +427,37 @@ def test_odd_engine_sizes(tmp_path, dtype):
     for s in slots:
         eng.release(s)
     eng.cache.check()
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_both_arrangements_of_the_parallel_block(tmp_path, which, monkeypatch):
+    """Decode steps over few keys run the feed-forward beside the mixer and end in the mixer's output
+    product; over many keys the two output projections are one product.  Both against the plain model,
+    with the threshold moved so that the tiny models take each."""
+    from qstream_b200.parts import block
+    folder, cfg = make_folder(tmp_path, which, "bfloat16")
+    rng = np.random.default_rng(77)
+    prompts = [random_tokens(rng, n, cfg.vocab_size) for n in (70, 9, 41)]
+    refs = [plain_logits(folder, p) for p in prompts]
+    outs = {}
+    for keys in (0, 1 << 30):
+        monkeypatch.setattr(block, "SIDE_BRANCH_MAX_KEYS", keys)
+        eng = engine_for(folder, "bfloat16")
+        assert all(b.fused_weight is not None for b in eng.model.blocks)
+        slots = [eng.acquire() for _ in prompts]
+        heads = [len(p) - 8 for p in prompts]
+        rows = [[eng.step([s], [p[:h]], [all_places(h)]).cpu().numpy()] for s, p, h in zip(slots, prompts, heads)]
+        for t in range(8):
+            got = eng.step(slots, [[p[h + t]] for p, h in zip(prompts, heads)], [[0]] * len(prompts)).cpu().numpy()
+            for i in range(len(prompts)):
+                rows[i].append(got[i:i + 1])
+        eng.check_status()
+        for i, ref in enumerate(refs):
+            assert_logits_close(np.concatenate(rows[i]), ref, "bfloat16", f"{which} keys<={keys} request {i}")
+        outs[keys] = [np.concatenate(r) for r in rows]
+        for s in slots:
+            eng.release(s)
+        eng.cache.check()
+    # the two arrangements differ by the rounding of one intermediate, not more
+    for a, b in zip(outs[0], outs[1 << 30]):
+        assert np.abs(a - b).max() <= 0.03 * np.abs(a).max()
