@@ -476,7 +476,7 @@ def per_kernel(shape, layers, pk, batch, ctx, prefill_tokens=2048, repeats=56):
             m = blocks[i].mixer
             view = step.kv(i)
             ops.rope_store(qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:], H, H, dh, m.position.rotary_dim, m.position.fused_table,
-                           sb.tok_slot, sb.tok_pos, view.page_table, view.page_tokens, view.k, view.v, step.status)
+                           sb.tok_slot, sb.tok_pos, view.page_table, view.page_tokens, view.k, view.v, step.status, settled=True)
         timed(f"{tag} rotary + cache write", rope, bytes_=T * 3 * D * 2 + T * 2 * D * 2)
 
         def attend(i):

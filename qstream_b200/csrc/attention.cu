@@ -99,18 +99,28 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_
                                       const int32_t* __restrict__ tok_slot, const int32_t* __restrict__ tok_pos,
                                       const int32_t* __restrict__ page_table, int max_pages, int page_shift,
                                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                                      int32_t* __restrict__ status) {
+                                      int32_t* __restrict__ status, int settled) {
     grid_dep_launch();
-    grid_dep_wait();
+    // `settled`: the step's slots, positions and pages and the table of angles were complete before the
+    // previous kernel of the stream began.  Then they are fetched (the table's row only as far as L2) while
+    // that kernel still runs.
+    if (!settled) grid_dep_wait();
     const int t = blockIdx.x;
     const int tid = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
     const int slot = tok_slot[t];
-    if (slot < 0) return;
     const int pos = tok_pos[t];
-    const int page_tokens = 1 << page_shift;
     const bool rotate = cos_sin != nullptr && R > 0;
-    if (rotate && (pos < 0 || pos >= max_pos)) { if (threadIdx.x == 0) atomicExch(status, 1); return; }
-    const float* cs = rotate ? cos_sin + (size_t)pos * R : nullptr;
+    const bool pos_ok = !rotate || (pos >= 0 && pos < max_pos);
+    const float* cs = rotate && pos_ok ? cos_sin + (size_t)pos * R : nullptr;
+    int page = -1;
+    if (slot >= 0 && n_kv_heads > 0 && pos >= 0 && (pos >> page_shift) < max_pages)
+        page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
+    if (cs && slot >= 0 && threadIdx.x * 32 < R)
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(cs + threadIdx.x * 32));
+    if (settled) grid_dep_wait();
+    if (slot < 0) return;
+    const int page_tokens = 1 << page_shift;
+    if (!pos_ok) { if (threadIdx.x == 0) atomicExch(status, 1); return; }
     const int rc = R >> 3, hc = dh >> 3;                                 // 16-byte chunks of the rotary part / of a head
     if (q && rotate) {
         for (int e = tid; e < n_heads * rc; e += stride) {
@@ -120,7 +130,6 @@ __global__ void rope_store_vec_kernel(__nv_bfloat16* __restrict__ q, const __nv_
         }
     }
     if (n_kv_heads == 0) return;
-    const int page = page_table[(size_t)slot * max_pages + (pos >> page_shift)];
     if (page < 0) { if (threadIdx.x == 0) atomicExch(status, 2); return; }
     const size_t in_page = (size_t)(pos & (page_tokens - 1)) * dh;
     for (int e = tid; e < n_kv_heads * hc; e += stride) {
@@ -249,6 +258,8 @@ int launch_attention(void* out, const void* q, long long ldo, long long ldq, con
 
 }  // namespace
 
+// `settled` != 0: slots, positions, page table and the table of angles were complete before the previous kernel
+// of the stream began (they came by a copy, or from an earlier step), so the kernel may read them early.
 QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
                          long long ldq, long long ldk, long long ldv,
                          int n_heads, int n_kv_heads, int dh, int R,
@@ -256,7 +267,7 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
                          const int32_t* tok_slot, const int32_t* tok_pos,
                          const int32_t* page_table, int max_pages, int page_tokens,
                          void* k_cache, void* v_cache, int T_tokens, int32_t* status,
-                         cudaStream_t stream) {
+                         int settled, cudaStream_t stream) {
     if (T_tokens == 0) return QS_OK;
     QS_REQUIRE(T_tokens > 0 && n_heads >= 0 && n_kv_heads >= 0 && n_heads + n_kv_heads > 0 && dh > 0, "rope_store: bad sizes");
     QS_REQUIRE(n_kv_heads == 0 || (k && v && k_cache && v_cache), "rope_store: keys and values without a cache to keep them");
@@ -281,7 +292,7 @@ QS_API int qs_rope_store(void* q, const void* k, const void* v, int dtype,
         cudaError_t e = qs_launch_dependent(rope_store_vec_kernel, dim3(T_tokens, per), dim3(threads8), 0, stream,
             (__nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (size_t)ldq, (size_t)ldk, (size_t)ldv,
             n_heads, n_kv_heads, dh, R, cos_sin, max_pos, tok_slot, tok_pos, page_table, max_pages, shift,
-            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status);
+            (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, status, settled);
         if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "rope_store: %s", cudaGetErrorString(e));
         return qs_check_launch("rope_store");
     }

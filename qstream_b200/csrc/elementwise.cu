@@ -101,14 +101,27 @@ __global__ void layernorm_kernel(T* __restrict__ out, const T* __restrict__ x,
 // kept in registers as NV 16-byte pieces per thread (width <= 1024 * NV), all of a thread's loads in
 // flight at once, statistics by the block's fixed-order sum.  At 40 registers sixteen blocks share an SM,
 // so 2,048 rows are one wave.  (One warp per row with the whole row in a lane's registers, 160 of them,
-// moved 1.5 TB/s on 2,048 rows of 4,096.)
-template <int NV>
+// moved 1.5 TB/s on 2,048 rows of 4,096.)  EARLY (few rows, a decode step): the thread's pieces of weight and
+// bias, which no kernel writes, are fetched before the wait for the previous kernel instead of after the two
+// sums, where their way from memory would be on the step's critical path; the arithmetic is the same.
+template <int NV, bool EARLY>
 __global__ void __launch_bounds__(128)
 layernorm_row_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                      const void* __restrict__ w, int w_dtype, const void* __restrict__ b, int b_dtype,
                      int D, float eps, size_t ldx, size_t ldo) {
     __shared__ float scratch[33];
     grid_dep_launch();
+    float we[EARLY ? NV : 1][8], be[EARLY ? NV : 1][8];
+    if (EARLY) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = (i * 128 + threadIdx.x) * 8;
+            if (c < D) {
+                load8_as_f32(w, w_dtype, c, we[i]);
+                if (b) load8_as_f32(b, b_dtype, c, be[i]);
+            }
+        }
+    }
     grid_dep_wait();
     const __nv_bfloat16* src = x + (size_t)blockIdx.x * ldx;
     uint4 raw[NV];
@@ -145,8 +158,13 @@ layernorm_row_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __res
             const uint32_t u[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
             uint32_t o[4];
             float wf[8], bf[8];
-            load8_as_f32(w, w_dtype, c, wf);
-            if (b) load8_as_f32(b, b_dtype, c, bf);
+            if (EARLY) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { wf[j] = we[i][j]; bf[j] = be[i][j]; }
+            } else {
+                load8_as_f32(w, w_dtype, c, wf);
+                if (b) load8_as_f32(b, b_dtype, c, bf);
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 float y0 = (__uint_as_float(u[j] << 16) - mean) * rstd * wf[2 * j];
@@ -162,7 +180,7 @@ layernorm_row_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __res
 
 QS_API int qs_layernorm(void* out, const void* x, int dtype, const void* w, int w_dtype,
                         const void* b, int b_dtype, int rows, int D, float eps,
-                        long long ldx, long long ldo, cudaStream_t stream) {
+                        long long ldx, long long ldo, int settled, cudaStream_t stream) {
     if (rows == 0) return QS_OK;
     QS_REQUIRE(rows > 0 && D > 0, "layernorm: bad sizes rows=%d D=%d", rows, D);
     // bfloat16 rows of 16-byte pieces: the row in registers, whatever the number of rows (prefill and decode
@@ -171,9 +189,11 @@ QS_API int qs_layernorm(void* out, const void* x, int dtype, const void* w, int 
         ((uintptr_t)x % 16) == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)w % (w_dtype == QS_F32 ? 32 : 16)) == 0 &&
         (!b || ((uintptr_t)b % (b_dtype == QS_F32 ? 32 : 16)) == 0)) {
         const int nv = (D + 1023) / 1024;
-#define GO(NV) qs_launch_dependent(layernorm_row_kernel<NV>, dim3(rows), dim3(128), 0, stream, (__nv_bfloat16*)out, \
+#define GO1(NV, EARLY) qs_launch_dependent(layernorm_row_kernel<NV, EARLY>, dim3(rows), dim3(128), 0, stream, (__nv_bfloat16*)out, \
             (const __nv_bfloat16*)x, w, w_dtype, b, b_dtype, D, eps, (size_t)ldx, (size_t)ldo)
+#define GO(NV) do { if (rows <= 64 && settled) GO1(NV, true); else GO1(NV, false); } while (0)
         if (nv <= 1) GO(1); else if (nv <= 2) GO(2); else if (nv <= 4) GO(4); else GO(8);
+#undef GO1
 #undef GO
         return qs_check_launch("layernorm");
     }

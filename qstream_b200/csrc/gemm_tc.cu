@@ -595,6 +595,24 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             left -= n;
             const int buf = seg & 1;
             const int feat = r < tile_rows ? tile * tile_rows + r : ep.N;       // rows past the tile's height are not stored
+            // What the epilogue reads besides the sums is fetched before the wait for them, so that its way from
+            // memory is not the kernel's tail: the bias and, with at most 16 tokens, the residuals' pieces.
+            const float bias_v = (feat < ep.N && ep.bias) ? load_as_f32(ep.bias, ep.bias_dtype, feat) : 0.f;
+            const int sub = lane & 7;
+            const int group_row = r - sub;                                    // the group's first TMEM lane
+            const int group_feat = tile * tile_rows + group_row;
+            const bool group_ok = group_row < tile_rows && group_feat < ep.N;  // all eight or none (multiples of 8)
+            constexpr bool EARLY_RES = BN == CH;
+            uint4 early1[EARLY_RES ? CH / 8 : 1], early2[EARLY_RES ? CH / 8 : 1];
+            if (EARLY_RES && vec_ok && group_ok) {
+#pragma unroll
+                for (int blk = 0; blk < CH / 8; ++blk) {
+                    const int m = blk * 8 + sub;
+                    if (m >= ep.M) continue;
+                    if (ep.res1) early1[blk] = *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + group_feat);
+                    if (ep.res2) early2[blk] = *reinterpret_cast<const uint4*>(ep.res2 + (size_t)m * ep.ldr + group_feat);
+                }
+            }
             if (!wait_or_abort(&acc_full[buf], (seg >> 1) & 1, aborted)) { atomicExch(status, 134); *aborted = 1; break; }
             tc_fence_after_sync();
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
@@ -611,11 +629,6 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             // lanes transpose 8 x 8 blocks by shuffles: a lane then holds eight neighbouring features of one
             // token and stores them at once.  Bias and activation come before the transpose (they go by
             // feature), residuals and the one rounding after it.
-            const float bias_v = (feat < ep.N && ep.bias) ? load_as_f32(ep.bias, ep.bias_dtype, feat) : 0.f;
-            const int sub = lane & 7;
-            const int group_row = r - sub;                                    // the group's first TMEM lane
-            const int group_feat = tile * tile_rows + group_row;
-            const bool group_ok = group_row < tile_rows && group_feat < ep.N;  // all eight or none (multiples of 8)
             auto emit = [&](int c, const float (&v)[CH]) {
                 const int m0 = c * CH;
                 if (vec_ok) {
@@ -641,13 +654,15 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
                         for (int i = 0; i < 8; ++i) x[i] = y[blk * 8 + i];
                         if (ep.res1) {
-                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + group_feat);
+                            const uint4 rr = EARLY_RES ? early1[EARLY_RES ? blk : 0]
+                                                       : *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + group_feat);
                             const uint32_t w4[4] = {rr.x, rr.y, rr.z, rr.w};
 #pragma unroll
                             for (int i = 0; i < 4; ++i) { x[2 * i] += __uint_as_float(w4[i] << 16); x[2 * i + 1] += __uint_as_float(w4[i] & 0xffff0000u); }
                         }
                         if (ep.res2) {
-                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res2 + (size_t)m * ep.ldr + group_feat);
+                            const uint4 rr = EARLY_RES ? early2[EARLY_RES ? blk : 0]
+                                                       : *reinterpret_cast<const uint4*>(ep.res2 + (size_t)m * ep.ldr + group_feat);
                             const uint32_t w4[4] = {rr.x, rr.y, rr.z, rr.w};
 #pragma unroll
                             for (int i = 0; i < 4; ++i) { x[2 * i] += __uint_as_float(w4[i] << 16); x[2 * i + 1] += __uint_as_float(w4[i] & 0xffff0000u); }

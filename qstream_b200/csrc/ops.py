@@ -25,14 +25,14 @@ _SIGNATURES = {
     "qs_abi_version": ([], c_int),
     "qs_embedding": ([c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p], c_int),
     "qs_layernorm": ([c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
-                      c_longlong, c_longlong, c_void_p], c_int),
+                      c_longlong, c_longlong, c_int, c_void_p], c_int),
     "qs_gather_rows": ([c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p], c_int),
     "qs_add": ([c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p], c_int),
     "qs_linear_simt": ([c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
                         c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p], c_int),
     "qs_rope_store": ([c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_longlong,
                        c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                       c_void_p, c_void_p, c_int, c_void_p, c_void_p], c_int),
+                       c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p], c_int),
     "qs_attention": ([c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                       c_void_p], c_int),
@@ -159,7 +159,9 @@ def embedding(table: torch.Tensor, tokens: torch.Tensor, out_dtype: torch.dtype)
     return out
 
 
-def layernorm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float, out=None) -> torch.Tensor:
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float, out=None, settled=False) -> torch.Tensor:
+    """`settled`: weight and bias were complete before the previous kernel of the stream began (a model's
+    are); the kernel then fetches them while that kernel still runs."""
     rows, D, ldx = _rows(x)
     if out is None:
         out = torch.empty((rows, D), dtype=x.dtype, device=x.device)
@@ -168,7 +170,7 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, bias, eps: float, out=None)
         raise QStreamError(QsError.INVALID_INPUT, f"layernorm: width {D} but weight {tuple(weight.shape)}")
     check(library().qs_layernorm(ptr(out), ptr(x), dtype_code(x), ptr(weight), dtype_code(weight),
                                  ptr(bias), dtype_code(bias) if bias is not None else 0, rows, D,
-                                 float(eps), ldx, ldo, stream()))
+                                 float(eps), ldx, ldo, int(bool(settled)), stream()))
     return out
 
 
@@ -218,9 +220,11 @@ def linear_simt(x, weight, bias=None, activation=None, residuals=(), out_dtype=N
 
 
 def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_slot, tok_pos,
-               page_table, page_tokens, k_cache, v_cache, status) -> None:
+               page_table, page_tokens, k_cache, v_cache, status, settled=False) -> None:
     """Rotate q (in place) and k, and write k and v into the paged cache entry.
-    k = v = None (n_kv_heads = 0): rotate q only (no page table is needed then)."""
+    k = v = None (n_kv_heads = 0): rotate q only (no page table is needed then).
+    `settled`: slots, positions, page table and the table of angles were complete before the previous kernel
+    of the stream began (a step's own are); the kernel then reads them early."""
     ref = k if k is not None else q
     T = ref.shape[0]
     max_pos = cos_sin.shape[0] if cos_sin is not None else 0
@@ -231,7 +235,7 @@ def rope_store(q, k, v, n_heads, n_kv_heads, head_dim, rotary_dim, cos_sin, tok_
         ptr(cos_sin), max_pos, _int32(tok_slot, "tok_slot"), _int32(tok_pos, "tok_pos"),
         _int32(page_table, "page_table") if page_table is not None else None,
         page_table.shape[1] if page_table is not None else 0, page_tokens, ptr(k_cache), ptr(v_cache), T,
-        ptr(status), stream()))
+        ptr(status), int(bool(settled)), stream()))
 
 
 def attention(q, n_heads, n_kv_heads, head_dim, scale, window, tok_slot, tok_pos, page_table,

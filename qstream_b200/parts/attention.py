@@ -90,7 +90,7 @@ class Attention(Mixer):
                 else:                                   # rotate q only: no keys of its own
                     ops.rope_store(q, None, None, s.n_heads, 0, s.head_dim, self.position.rotary_dim, table,
                                    b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, None, None,
-                                   step.status)
+                                   step.status, settled=True)
         else:
             k = qkv[:, hq:hq + hkv]
             v = qkv[:, hq + hkv:]
@@ -99,7 +99,7 @@ class Attention(Mixer):
             ops.rope_store(q, k, v, s.n_heads, s.n_kv_heads, s.head_dim,
                            getattr(self.position, "rotary_dim", 0) if table is not None else 0, table,
                            b.tok_slot, b.tok_pos, view.page_table, view.page_tokens, view.k, view.v,
-                           step.status)
+                           step.status, settled=True)     # a step's slots, positions and pages arrive before its first kernel
         return attend(q, s, step, view, out)
 
 

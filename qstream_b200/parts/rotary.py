@@ -35,7 +35,7 @@ class RotaryInterleaved(PositionEncoding):
         for x, heads in ((q, n_heads), (k, n_kv_heads)):
             if x is not None and heads > 0:
                 ops.rope_store(x, None, None, heads, 0, head_dim, self.rotary_dim, self.fused_table,
-                               b.tok_slot, b.tok_pos, None, 64, None, None, step.status)
+                               b.tok_slot, b.tok_pos, None, 64, None, None, step.status, settled=True)
 
 
 register("position", "rotary_interleaved", RotaryInterleaved)

@@ -49,6 +49,11 @@ def test_layernorm(dtype, D, eps, wdtype):
     np.testing.assert_allclose(f64(got), ref, **tol(dtype))
     got = ops.layernorm(x.cuda(), w.cuda(), None, eps)
     np.testing.assert_allclose(f64(got), P.layer_norm(f64(x), f64(w), None, eps), **tol(dtype))
+    # weights that are older than the stream's last kernel may be fetched before its end: the same bits
+    xd, wdev, bdev = x.cuda(), w.cuda(), b.cuda()
+    late = ops.layernorm(xd, wdev, bdev, eps)
+    torch.cuda.synchronize()
+    assert torch.equal(ops.layernorm(xd, wdev, bdev, eps, settled=True), late)
 
 
 @pytest.mark.parametrize("adt,wdt,cdt", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
@@ -120,12 +125,15 @@ def rope_table(max_pos, R, base=10000.0):
     return torch.stack([ang.cos(), ang.sin()], -1).float().contiguous().cuda()
 
 
+@pytest.mark.parametrize("settled", [False, True])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,Hkv,dh,R,window", [(4, 4, 16, 8, 0), (6, 2, 48, 48, 0), (2, 1, 80, 64, 0),
                                                 (3, 3, 256, 64, 0), (4, 2, 32, 16, 37), (2, 2, 16, 0, 64)])
-def test_rope_store_and_attention(dtype, H, Hkv, dh, R, window):
+def test_rope_store_and_attention(dtype, H, Hkv, dh, R, window, settled):
     """Prompts in one packed step, then some tokens one by one, through shuffled pages;
-    compared with the plain rotary + causal attention on whole sequences."""
+    compared with the plain rotary + causal attention on whole sequences.  `settled`: the kernel reads
+    slots, positions and pages before the previous kernel has ended (they are older than it here: the
+    test waits for the device before each call)."""
     lens = [1, 70, 130, 64]
     case = PagedCase(dtype, lens, H, Hkv, dh, seed=H * dh)
     table = rope_table(256, R) if R else None
@@ -134,7 +142,10 @@ def test_rope_store_and_attention(dtype, H, Hkv, dh, R, window):
 
     def run(ranges):
         q, k, v, slot, pos = case.packed(ranges)
-        ops.rope_store(q, k, v, H, Hkv, dh, R, table, slot, pos, table_dev, case.pt, case.k_cache, case.v_cache, case.status)
+        if settled:
+            torch.cuda.synchronize()
+        ops.rope_store(q, k, v, H, Hkv, dh, R, table, slot, pos, table_dev, case.pt, case.k_cache, case.v_cache, case.status,
+                       settled=settled)
         o = ops.attention(q, H, Hkv, dh, dh ** -0.5, window, slot, pos, table_dev, case.pt, case.k_cache, case.v_cache, case.status)
         row = 0
         for i, a, b in ranges:
