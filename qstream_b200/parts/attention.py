@@ -59,6 +59,11 @@ class Attention(Mixer):
         if spec.position is not None:
             self.position = part_class("position", spec.position.kind)(spec.position, {}, runtime)
 
+    @property
+    def cache_bytes_per_key(self) -> int:
+        """What one key of a sequence costs a decode step to read: its key and its value, all heads."""
+        return 2 * self.spec.n_kv_heads * self.spec.head_dim * self.w_qkv.element_size()
+
     def kv_need(self):
         if self.spec.shares_cache:
             return None

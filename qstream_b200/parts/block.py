@@ -62,9 +62,13 @@ class Arrangement(Part):
         return [self.mixer]
 
 
-# A decode step whose rows together hold at most this many keys (rows x the longest sequence) runs its
-# two branches side by side; beyond it the attention kernels are bound by memory like the products.
-SIDE_BRANCH_MAX_KEYS = 4096
+# A decode step runs a parallel block's two branches side by side while the keys and values its rows read
+# (rows x the longest sequence x the mixer's bytes per key) stay below this share of the feed-forward's
+# weights: then the attention kernels are bound by latency, beyond it by memory like the products.
+# Measured on a B200 against the one fused product, tokens a second: GPT-J-6B's sizes +7 to +13 % up to a share
+# of 0.25 (1 x 2,048 keys, 4 x 1,024, 8 x 512, 16 x 256), -3 to -5 % from 0.5 on; CodeGen-16B's +10 to +13 %
+# up to 0.17, +3 to +4 % at 0.33, +1 % at 0.67; CodeGen-2B's +12 to +14 % up to 0.2, +1 to +3 % at 0.4, -1.5 % at 0.8.
+SIDE_BRANCH_SHARE = 0.35
 
 
 class ParallelBlock(Arrangement):
@@ -95,6 +99,10 @@ class ParallelBlock(Arrangement):
                 # the parts keep views of the fused matrix, so the weights are held once
                 self.mixer.w_out = self.fused_weight[:, :self.k_mixer]
                 self.ffn.down = self.fused_weight[:, self.k_mixer:]
+                # the feed-forward's two matrices, taken as equal in size; a mixer that does not say what a key
+                # costs it never runs beside the feed-forward
+                self.ffn_bytes = 2 * self.ffn.down.numel() * self.fused_weight.element_size()
+                self.key_bytes = getattr(self.mixer, "cache_bytes_per_key", None)
 
     def forward(self, x, step, cache_id):
         h = self.norms["input"].forward(x)
@@ -105,9 +113,8 @@ class ParallelBlock(Arrangement):
         from .linear import linear
         b = step.batch
         side = getattr(step, "side_stream", None)
-        if side is not None and b.decode and h.shape[0] * (b.max_total or step.cache.max_context) <= SIDE_BRANCH_MAX_KEYS:
-            # Measured on a B200 at GPT-J-6B's sizes against the one fused product: 7 to 13 % more tokens a
-            # second up to 4,096 keys (1 x 2,048, 4 x 1,024, 8 x 512, 16 x 256), 3 to 5 % fewer from 8,192 on.
+        if (side is not None and b.decode and self.key_bytes is not None
+                and h.shape[0] * (b.max_total or step.cache.max_context) * self.key_bytes <= SIDE_BRANCH_SHARE * self.ffn_bytes):
             from .linear import beside_main_stream
             with beside_main_stream(side, h.device) as beside:
                 g = self.ffn.forward_hidden(h, step)

@@ -441,7 +441,7 @@ def test_both_arrangements_of_the_parallel_block(tmp_path, which, monkeypatch):
     refs = [plain_logits(folder, p) for p in prompts]
     outs = {}
     for keys in (0, 1 << 30):
-        monkeypatch.setattr(block, "SIDE_BRANCH_MAX_KEYS", keys)
+        monkeypatch.setattr(block, "SIDE_BRANCH_SHARE", float(keys))
         eng = engine_for(folder, "bfloat16")
         assert all(b.fused_weight is not None for b in eng.model.blocks)
         slots = [eng.acquire() for _ in prompts]
@@ -453,7 +453,7 @@ def test_both_arrangements_of_the_parallel_block(tmp_path, which, monkeypatch):
                 rows[i].append(got[i:i + 1])
         eng.check_status()
         for i, ref in enumerate(refs):
-            assert_logits_close(np.concatenate(rows[i]), ref, "bfloat16", f"{which} keys<={keys} request {i}")
+            assert_logits_close(np.concatenate(rows[i]), ref, "bfloat16", f"{which} share<={keys} request {i}")
         outs[keys] = [np.concatenate(r) for r in rows]
         for s in slots:
             eng.release(s)
