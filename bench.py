@@ -489,6 +489,12 @@ def per_kernel(shape, layers, pk, batch, ctx, prefill_tokens=2048, repeats=56):
               lambda i: linear(hidden, blocks[i].fused_weight, blocks[i].fused_bias, residuals=(x,)),
               bytes_=(D + F) * D * 2, flops=2 * T * (D + F) * D)
         if phase == "decode":
+            # the same two projections as the block runs them when the feed-forward goes beside the mixer
+            mm = torch.empty(T, D, dtype=torch.bfloat16, device="cuda")
+            timed(f"{tag} fc_out product alone", lambda i: linear(hidden[:, D:], blocks[i].fused_weight[:, D:], blocks[i].fused_bias, out=mm),
+                  bytes_=F * D * 2, flops=2 * T * F * D)
+            timed(f"{tag} out_proj product + residuals", lambda i: linear(hidden[:, :D], blocks[i].fused_weight[:, :D], None, residuals=(x, mm)),
+                  bytes_=D * D * 2, flops=2 * T * D * D)
             z = torch.randn(T, D, device="cuda", generator=rng).bfloat16()
             logits = model.head.forward(z)
             timed(f"{tag} lm_head product", lambda i: model.head.forward(z),
