@@ -223,9 +223,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // ----------------------------------------------------------------------------- persistent kernel on CTA pairs
 
 // per CTA and stage: 128 rows of A and its half of the PAIR_BN rows of W, 64 wide
+// Epilogue warps of the pair kernel: four, or eight (each TMEM lane quarter then has two warps that share the
+// tile's columns).  Eight were measured: a product of one round of tiles gains 7 % (256 x 16384 x 4096: 39 -> 36 us),
+// one whose k-ranges are cut loses 6 to 9 %, and 2,048-token products stay where they are or lose 2 %.
+constexpr int PAIR_EPILOGUE_THREADS = 128;
+constexpr int PAIR_THREADS = 64 + PAIR_EPILOGUE_THREADS;      // producer warp, MMA warp, epilogue warps
 template <int PAIR_BN> constexpr int pair_stage() { return BM * BK * 2 + (PAIR_BN / 2) * BK * 2; }
 template <int PAIR_BN> constexpr int pair_stages() { return SMEM_BUDGET_BIG / pair_stage<PAIR_BN>(); }
-template <int PAIR_BN> constexpr int pair_smem() { return pair_stages<PAIR_BN>() * pair_stage<PAIR_BN>() + 1024 + 512; }
+template <int PAIR_BN> constexpr int pair_smem() { return pair_stages<PAIR_BN>() * pair_stage<PAIR_BN>() + 1024 + 512 + PAIR_BN * 4; }
 
 // Like wait_or_abort, and it also gives up when any CTA of the grid has reported a failure.
 __device__ __forceinline__ bool wait_or_abort_grid(uint64_t* bar, uint32_t parity, volatile uint32_t* aborted,
@@ -245,7 +250,7 @@ __device__ __forceinline__ bool wait_or_abort_grid(uint64_t* bar, uint32_t parit
 // barrier; tcgen05.commit tells both CTAs when a stage or an accumulator may be used again; the other
 // CTA's epilogue warps signal the leader across the cluster.  No load uses multicast.
 template <int PAIR_BN>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const Epilogue ep, const int K, const int m_pairs, const int n_tiles, const int splits,
                     float* __restrict__ ws, int32_t* __restrict__ counters, int32_t* __restrict__ status) {
@@ -261,6 +266,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile uint32_t* aborted = tmem_slot + 1;
     volatile uint32_t* last_flag = tmem_slot + 2;
+    float* s_bias = reinterpret_cast<float*>(smem + PAIR_STAGES * PAIR_STAGE + 512);     // [PAIR_BN]: the tile's bias
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
@@ -272,7 +278,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 256); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * PAIR_EPILOGUE_THREADS); }
         *aborted = 0;
         mbar_fence_init();
         prefetch_tensormap(&map_a);
@@ -285,9 +291,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    grid_dep_launch();                                // the next kernel may set itself up beside this one
     if (warp == 0) {
         if (elect_one()) {
+            // Launched as a programmatic dependent: the weights, which no kernel writes, fill the ring while the
+            // previous kernel may still be running; the rows of A of those stages follow once it has completed.
             uint32_t it = 0;
+            bool waited = false;
+            int late_kb[PAIR_STAGES], late_m0[PAIR_STAGES];
+            auto catch_up = [&]() {
+                grid_dep_wait();
+                waited = true;
+                const int n_late = (int)min(it, (uint32_t)PAIR_STAGES);
+                for (int s = 0; s < n_late; ++s)
+                    tma_load_2d_pair(smem + s * PAIR_STAGE, &map_a, &full[s], late_kb[s] * BK, late_m0[s]);
+            };
             for (int t = pair; t < total_tiles && !*aborted; t += n_pairs_grid) {
                 const int tile = t / splits, part = t - tile * splits;
                 const int m0 = (tile % m_pairs) * 2 * BM + (int)rank * BM;
@@ -295,13 +313,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int kb_end = (int)((long long)(part + 1) * num_kb / splits);
                 for (int kb = (int)((long long)part * num_kb / splits); kb < kb_end; ++kb, ++it) {
                     const int s = it % PAIR_STAGES;
+                    if (!waited && it >= (uint32_t)PAIR_STAGES) catch_up();
                     if (!wait_or_abort_grid(&empty[s], ((it / PAIR_STAGES) & 1) ^ 1, aborted, status)) { atomicExch(status, 151); *aborted = 1; break; }
                     uint8_t* st = smem + s * PAIR_STAGE;
                     if (rank == 0) mbar_expect_tx(&full[s], 2 * PAIR_STAGE);     // both CTAs' bytes
-                    tma_load_2d_pair(st, &map_a, &full[s], kb * BK, m0);
+                    if (waited) tma_load_2d_pair(st, &map_a, &full[s], kb * BK, m0);
+                    else { late_kb[s] = kb; late_m0[s] = m0; }
                     tma_load_2d_pair(st + BM * BK * 2, &map_w, &full[s], kb * BK, n0);
                 }
             }
+            if (!waited) catch_up();
         }
     } else if (warp == 1) {
         if (rank == 0 && elect_one()) {
@@ -330,20 +351,44 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     } else {
-        const int quad = warp & 3;
+        // a warp reads the quarter of the TMEM lanes that its number allows (warp % 4) and its share of the columns
+        const int quad = warp & 3, half = (warp - 2) >> 2;
         const int r = quad * 32 + lane;
+        constexpr int HALF_CHUNKS = PAIR_BN / 32 / (PAIR_EPILOGUE_THREADS / 128);      // chunks of 32 columns per warp
         const bool vec_ok = ep.c_dtype == QS_BF16 && (ep.ldc % 8) == 0 && ((uintptr_t)ep.C % 16) == 0 &&
                             (!ep.res1 || ((ep.ldr % 8) == 0 && ((uintptr_t)ep.res1 % 16) == 0)) &&
                             (!ep.res2 || ((uintptr_t)ep.res2 % 16) == 0);
-        const bool bias_vec = ep.bias && ((uintptr_t)ep.bias % 32) == 0;
         const uint32_t leader_acc_empty[2] = {map_to_cta(&acc_empty[0], 0), map_to_cta(&acc_empty[1], 0)};
+        grid_dep_wait();                                  // residuals, outputs and the workspace belong to earlier kernels until now
         int i = 0;
         for (int t = pair; t < total_tiles; t += n_pairs_grid, ++i) {
             const int buf = i & 1;
             const int tile = t / splits, part = t - tile * splits;
             const int m = (tile % m_pairs) * 2 * BM + (int)rank * BM + r, n0 = (tile / m_pairs) * PAIR_BN;
+            // The tile's bias goes to shared memory once, before the wait for the sums: read per group of
+            // columns from global memory it cost every thread 32 round trips in a row (a warp is alone on
+            // its scheduler here, and loads do not move across the stores between them): 9 of the 21 us that
+            // a 256 x 256 tile's epilogue took.
+            if (*aborted) break;                                         // a thread that gave up a wait meets no barrier again
+            if (ep.bias) {
+                asm volatile("bar.sync 1, %0;" ::"n"(PAIR_EPILOGUE_THREADS) : "memory");            // the previous tile's readers are done
+                for (int j = threadIdx.x - 64; j < PAIR_BN; j += PAIR_EPILOGUE_THREADS)
+                    s_bias[j] = n0 + j < ep.N ? load_as_f32(ep.bias, ep.bias_dtype, n0 + j) : 0.f;
+                asm volatile("bar.sync 1, %0;" ::"n"(PAIR_EPILOGUE_THREADS) : "memory");
+            }
             if (!wait_or_abort_grid(&acc_full[buf], (i >> 1) & 1, aborted, status)) { atomicExch(status, 154); *aborted = 1; break; }
             tc_fence_after_sync();
+            // this thread's pieces of the residuals for 32 columns, asked for before the sums are waited for
+            uint4 pre1[4], pre2[4];
+            auto prefetch = [&](int c) {
+                const int nc = n0 + c * 32;
+                if (m >= ep.M || !(vec_ok && nc + 32 <= ep.N)) return;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    if (ep.res1) pre1[g] = *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + nc + g * 8);
+                    if (ep.res2) pre2[g] = *reinterpret_cast<const uint4*>(ep.res2 + (size_t)m * ep.ldr + nc + g * 8);
+                }
+            };
             // bias, activation, residuals and the store of 32 columns of this thread's row
             auto finish = [&](int c, const uint32_t (&raw)[32]) {
                 const int nc = n0 + c * 32;
@@ -354,11 +399,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int g = 0; g < 4; ++g) {
                         float v[8], bv[8];
                         if (ep.bias) {
-                            if (bias_vec) load8_as_f32(ep.bias, ep.bias_dtype, nc + g * 8, bv);
-                            else {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) bv[j] = load_as_f32(ep.bias, ep.bias_dtype, nc + g * 8 + j);
-                            }
+                            const float4 b0 = *reinterpret_cast<const float4*>(s_bias + c * 32 + g * 8);
+                            const float4 b1 = *reinterpret_cast<const float4*>(s_bias + c * 32 + g * 8 + 4);
+                            bv[0] = b0.x; bv[1] = b0.y; bv[2] = b0.z; bv[3] = b0.w;
+                            bv[4] = b1.x; bv[5] = b1.y; bv[6] = b1.z; bv[7] = b1.w;
                         }
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -367,13 +411,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             v[j] = apply_activation_fast(x, ep.act);
                         }
                         if (ep.res1) {
-                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res1 + (size_t)m * ep.ldr + nc + g * 8);
+                            const uint4 rr = pre1[g];
                             const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
 #pragma unroll
                             for (int j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u); }
                         }
                         if (ep.res2) {
-                            const uint4 rr = *reinterpret_cast<const uint4*>(ep.res2 + (size_t)m * ep.ldr + nc + g * 8);
+                            const uint4 rr = pre2[g];
                             const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
 #pragma unroll
                             for (int j = 0; j < 4; ++j) { v[2 * j] += __uint_as_float(w[j] << 16); v[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u); }
@@ -394,8 +438,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             };
             if (splits == 1) {
 #pragma unroll 1
-                for (int c = 0; c < PAIR_BN / 32; ++c) {
+                for (int c = half * HALF_CHUNKS; c < (half + 1) * HALF_CHUNKS; ++c) {
                     uint32_t raw[32];
+                    prefetch(c);
                     tmem_load_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * PAIR_BN + c * 32), raw);
                     tmem_load_wait();
                     finish(c, raw);
@@ -408,7 +453,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // parts in the order of their k-ranges and finishes the tile.  Nobody waits for anybody.
                 float* mine = ws + ((size_t)t * 2 + rank) * BM * PAIR_BN;
 #pragma unroll 1
-                for (int c = 0; c < PAIR_BN / 32; ++c) {
+                for (int c = half * HALF_CHUNKS; c < (half + 1) * HALF_CHUNKS; ++c) {
                     uint32_t raw[32];
                     tmem_load_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * PAIR_BN + c * 32), raw);
                     tmem_load_wait();
@@ -418,20 +463,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tc_fence_before_sync();
                 mbar_arrive_cluster(leader_acc_empty[buf]);
                 __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (*aborted) break;
+                asm volatile("bar.sync 1, %0;" ::"n"(PAIR_EPILOGUE_THREADS) : "memory");
                 if (threadIdx.x == 64) {
                     const int prev = atomicAdd(&counters[tile * 2 + (int)rank], 1);
                     const bool last = prev == splits - 1;
                     *last_flag = last ? 1u : 0u;
                     if (last) counters[tile * 2 + (int)rank] = 0;     // ready for the next launch
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(PAIR_EPILOGUE_THREADS) : "memory");
                 if (*last_flag) {
                     __threadfence();
                     const float* first = ws + ((size_t)(tile * splits) * 2 + rank) * BM * PAIR_BN;
 #pragma unroll 1
-                    for (int c = 0; c < PAIR_BN / 32; ++c) {
+                    for (int c = half * HALF_CHUNKS; c < (half + 1) * HALF_CHUNKS; ++c) {
                         float v[32];
+                        prefetch(c);
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] = 0.f;
                         for (int p = 0; p < splits; ++p) {
@@ -445,7 +492,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         finish(c, raw);
                     }
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");        // last_flag is read by all before it is reused
+                asm volatile("bar.sync 1, %0;" ::"n"(PAIR_EPILOGUE_THREADS) : "memory");        // last_flag is read by all before it is reused
                 (void)part;
             }
         }
@@ -888,7 +935,7 @@ int pair_max_clusters() {
         if (cudaFuncSetAttribute(gemm_tc_pair_kernel<PAIR_BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  pair_smem<PAIR_BN>()) == cudaSuccess) {
             cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(2); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = pair_smem<PAIR_BN>();
+            cfg.gridDim = dim3(2); cfg.blockDim = dim3(PAIR_THREADS); cfg.dynamicSmemBytes = pair_smem<PAIR_BN>();
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
@@ -914,11 +961,13 @@ int launch_pair(const CUtensorMap& ma, const void* W, long long ldw, const Epilo
     const long long total = tiles * splits;
     const int clusters = (int)(total < max_clusters ? total : max_clusters);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = pair_smem<PAIR_BN>(); cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(PAIR_THREADS); cfg.dynamicSmemBytes = pair_smem<PAIR_BN>(); cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<PAIR_BN>, ma, mw, ep, K, m_pairs, n_tiles, (int)splits,
                                        ws, counters, status);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc pair: %s", cudaGetErrorString(e));
