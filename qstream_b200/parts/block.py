@@ -116,9 +116,11 @@ class ParallelBlock(Arrangement):
         if (side is not None and b.decode and self.key_bytes is not None
                 and h.shape[0] * (b.max_total or step.cache.max_context) * self.key_bytes <= SIDE_BRANCH_SHARE * self.ffn_bytes):
             from .linear import beside_main_stream
+            # m is read on the main stream, so it comes from the main stream's memory; g lives on the second stream only
+            m = torch.empty((h.shape[0], self.fused_weight.shape[0]), dtype=h.dtype, device=h.device)
             with beside_main_stream(side, h.device) as beside:
                 g = self.ffn.forward_hidden(h, step)
-                m = linear(g, self.fused_weight[:, self.k_mixer:], self.fused_bias)
+                linear(g, self.fused_weight[:, self.k_mixer:], self.fused_bias, out=m)
             o = self.mixer.forward_hidden(h, step, cache_id)
             beside.join()
             return linear(o, self.fused_weight[:, :self.k_mixer], None, residuals=(x, m))
