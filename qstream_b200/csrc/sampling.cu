@@ -10,6 +10,7 @@
 namespace {
 
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int SAMPLE_LIST = 1024;            // most elements that the sampler's short way lists after top-k
 
 // Monotone map of a float to an unsigned key (larger float -> larger key).
 __device__ __forceinline__ uint32_t order_key(float v) {
@@ -93,14 +94,25 @@ argmax_kernel(int32_t* __restrict__ out, const float* __restrict__ logits, int V
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, int V, size_t ld,
                                       const int32_t* __restrict__ recent, int window,
                                       const int32_t* __restrict__ n_recent, float penalty) {
+    // One thread per entry of the window.  The thread of a token's first occurrence applies the penalty as
+    // often as the token occurs, one division or multiplication after the other as a walk through the window
+    // would, so the result is the same bits; the tokens' loads and stores go side by side instead of one
+    // round trip after the other (64 entries: some 45 us in one thread).
     const int row = blockIdx.x;
-    if (threadIdx.x != 0) return;
     float* x = logits + (size_t)row * ld;
     const int n = min(n_recent[row], window);
-    for (int i = 0; i < n; ++i) {
-        const int t = recent[(size_t)row * window + i];
+    const int32_t* mine = recent + (size_t)row * window;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int t = mine[i];
         if (t < 0 || t >= V) continue;
-        x[t] = x[t] > 0.f ? x[t] / penalty : x[t] * penalty;
+        bool first = true;
+        for (int j = 0; j < i; ++j) first = first && mine[j] != t;
+        if (!first) continue;
+        int times = 0;
+        for (int j = i; j < n; ++j) times += mine[j] == t ? 1 : 0;
+        float v = x[t];
+        for (int c = 0; c < times; ++c) v = v > 0.f ? v / penalty : v * penalty;
+        x[t] = v;
     }
 }
 
@@ -118,18 +130,114 @@ sample_kernel(int32_t* __restrict__ out, const float* __restrict__ logits, int V
     __shared__ float chunk_sum[SAMPLE_THREADS];
     __shared__ int chunk_ties[SAMPLE_THREADS];
     __shared__ int result;
+    __shared__ int hist[256];
+    __shared__ uint32_t sel_prefix;
+    __shared__ int sel_remaining, list_n, list_kept;
     const float* x = logits + (size_t)blockIdx.x * ld;
     const float inv_t = temperature == 1.0f ? 1.0f : 1.0f / temperature;
     const int tid = threadIdx.x;
 
-    // the k-th largest key
+    // The k-th largest key, one byte of it per pass over the row: a count of the candidates' next byte
+    // (integers: the order of the additions does not matter), then the byte at which the count from the top
+    // reaches what is still wanted.  (One bit per pass, 32 passes with a sum over the block each, took 150 us
+    // of a 300 us kernel at a vocabulary of 50,400.)
     uint32_t k_key = 0;                              // keep everything
     if (top_k > 0 && top_k < V) {
-        for (int bit = 31; bit >= 0; --bit) {
-            const uint32_t trial = k_key | (1u << bit);
-            float cnt = 0.f;
-            for (int i = tid; i < V; i += blockDim.x) cnt += order_key(x[i] * inv_t) >= trial ? 1.f : 0.f;
-            if (block_sum(cnt, scratch) >= (float)top_k) k_key = trial;
+        if (tid == 0) { sel_prefix = 0; sel_remaining = top_k; }
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            if (tid < 256) hist[tid] = 0;
+            __syncthreads();
+            const uint32_t prefix = sel_prefix;
+            for (int i = tid; i < V; i += blockDim.x) {
+                const uint32_t key = order_key(x[i] * inv_t);
+                if (shift == 24 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(key >> shift) & 255u], 1);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int want = sel_remaining, d = 255;
+                for (; d > 0; --d) {
+                    if (hist[d] >= want) break;
+                    want -= hist[d];
+                }
+                sel_prefix = prefix | ((uint32_t)d << shift);
+                sel_remaining = want;
+            }
+            __syncthreads();
+        }
+        k_key = sel_prefix;
+
+        // The elements that top-k keeps (k of them, and the ties at the k-th value) are few: they are listed,
+        // put in the order that top-p wants (falling value, equal values by rising index), and one thread does
+        // the sums over them as src/sampling.c:121-211 does, in 32-bit.  A list that overflows (a very large
+        // k, or thousands of equal logits) goes the general way below.
+        __shared__ float l_y[SAMPLE_LIST], s_y[SAMPLE_LIST], s_w[SAMPLE_LIST];
+        __shared__ int l_i[SAMPLE_LIST], s_i[SAMPLE_LIST];
+        if (tid == 0) list_n = 0;
+        __syncthreads();
+        for (int i = tid; i < V; i += blockDim.x) {
+            const float y = x[i] * inv_t;
+            if (order_key(y) >= k_key) {
+                const int at = atomicAdd(&list_n, 1);
+                if (at < SAMPLE_LIST) { l_y[at] = y; l_i[at] = i; }
+            }
+        }
+        __syncthreads();
+        const int m = list_n;
+        if (m <= SAMPLE_LIST) {
+            for (int a = tid; a < m; a += blockDim.x) {              // rank in (value falling, index rising)
+                const uint32_t ka = order_key(l_y[a]);
+                const int ia = l_i[a];
+                int rank = 0;
+                for (int b = 0; b < m; ++b) {
+                    const uint32_t kb = order_key(l_y[b]);
+                    rank += (kb > ka || (kb == ka && l_i[b] < ia)) ? 1 : 0;
+                }
+                s_y[rank] = l_y[a];
+                s_i[rank] = ia;
+            }
+            __syncthreads();
+            const float top = s_y[0];
+            for (int a = tid; a < m; a += blockDim.x) s_w[a] = expf(s_y[a] - top);
+            __syncthreads();
+            if (tid == 0) {
+                int kept = m;
+                float z = 0.f;
+                for (int a = 0; a < m; ++a) z += s_w[a];
+                if (top_p > 0.f && top_p < 1.f && z > 0.f) {
+                    const float limit = top_p * z;
+                    float run = 0.f;
+                    for (int a = 0; a < m; ++a) {
+                        run += s_w[a];
+                        if (run > limit) { kept = a + 1; break; }
+                    }
+                }
+                list_kept = kept;
+            }
+            __syncthreads();
+            const int kept = list_kept;
+            for (int a = tid; a < kept; a += blockDim.x) {           // the kept ones by rising index
+                const int ia = s_i[a];
+                int rank = 0;
+                for (int b = 0; b < kept; ++b) rank += s_i[b] < ia ? 1 : 0;
+                l_i[rank] = ia;
+                l_y[rank] = s_w[a];
+            }
+            __syncthreads();
+            if (tid == 0) {
+                float total = 0.f;
+                for (int a = 0; a < kept; ++a) total += l_y[a];
+                const float target = draws[blockIdx.x] * total;
+                int r = -1, last = 0;
+                float run = 0.f;
+                for (int a = 0; a < kept; ++a) {
+                    if (!(l_y[a] > 0.f)) continue;                   // a weight of zero (or NaN) is never drawn
+                    last = l_i[a];
+                    run += l_y[a];
+                    if (r < 0 && run >= target) r = l_i[a];
+                }
+                out[blockIdx.x] = r >= 0 ? r : last;                 // none reached the target: the last kept, else 0
+            }
+            return;
         }
     }
 
@@ -251,7 +359,7 @@ QS_API int qs_repeat_penalty(float* logits, int rows, int V, long long ld, const
                              int window, const int32_t* n_recent, float penalty, cudaStream_t stream) {
     if (rows == 0 || penalty <= 1.0f) return QS_OK;
     QS_REQUIRE(rows > 0 && V > 0 && window > 0, "repeat_penalty: bad sizes");
-    repeat_penalty_kernel<<<rows, 32, 0, stream>>>(logits, V, (size_t)ld, recent, window, n_recent, penalty);
+    repeat_penalty_kernel<<<rows, 64, 0, stream>>>(logits, V, (size_t)ld, recent, window, n_recent, penalty);
     return qs_check_launch("repeat_penalty");
 }
 

@@ -256,7 +256,8 @@ def test_repeat_penalty():
 
 @pytest.mark.parametrize("V", [320, 50400])
 @pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 0, 1.0), (0.7, 40, 0.9), (1.3, 5, 1.0),
-                                                     (0.9, 0, 0.5), (0.5, 1, 1.0)])
+                                                     (0.9, 0, 0.5), (0.5, 1, 1.0), (1.0, 1000, 0.97), (0.9, 3000, 0.95),
+                                                     (1.1, 300, 1.0)])
 def test_sample_against_plain(V, temperature, top_k, top_p):
     """The chosen token's CDF interval in the plain pipeline must contain the draw (a
     little widened: 32-bit sums in another order)."""
@@ -279,6 +280,42 @@ def test_sample_against_plain(V, temperature, top_k, top_p):
         assert probs[got[r]] > 0, f"row {r}: token {got[r]} was filtered out"
         lo, hi = P.cdf_interval(probs, got[r])
         assert lo - 1e-4 <= float(draws[r]) <= hi + 1e-4, (r, got[r], lo, hi, float(draws[r]))
+
+
+def test_repeat_penalty_of_a_full_window_with_repeats():
+    g = torch.Generator().manual_seed(5)
+    V = 1000
+    x = torch.randn(3, V, generator=g) * 3
+    recent = torch.randint(0, 40, (3, 64), generator=g).to(torch.int32)       # 64 entries over 40 tokens: many repeats
+    recent[1, 5] = -1                                                          # entries outside the vocabulary are skipped
+    recent[1, 6] = V
+    count = torch.tensor([64, 64, 17], dtype=torch.int32)
+    d = x.cuda()
+    ops.repeat_penalty(d, recent.cuda(), count.cuda(), 1.3)
+    for r in range(3):
+        toks = [t for t in recent[r, :count[r]].tolist() if 0 <= t < V]
+        ref = P.apply_repeat_penalty(x[r].double().numpy(), toks, 1.3)
+        np.testing.assert_allclose(d[r].cpu().numpy(), ref, rtol=1e-5)
+
+
+def test_sample_top_k_keeps_the_ties_at_the_kth_value():
+    x = torch.full((1, 3000), -5.0)
+    x[0, [7, 100, 2500, 2999]] = torch.tensor([3.0, 2.0, 2.0, 2.0])          # k = 2: the three equal seconds all stay
+    got = set()
+    for r in np.linspace(0.0, 0.9999, 60):
+        got.add(ops.sample(x.cuda(), 1.0, 2, 1.0, torch.tensor([r], dtype=torch.float32).cuda()).item())
+    assert got == {7, 100, 2500, 2999}
+    # with top-p on top: 3.0 holds 0.475 of the four's mass, so p = 0.6 keeps it and the first of the equal ones
+    got = set()
+    for r in np.linspace(0.0, 0.9999, 60):
+        got.add(ops.sample(x.cuda(), 1.0, 2, 0.6, torch.tensor([r], dtype=torch.float32).cuda()).item())
+    assert got == {7, 100}
+    # all equal: every element ties at the k-th value; p = 0.3 of eight keeps the first three by index
+    z = torch.zeros(1, 8)
+    got = set()
+    for r in np.linspace(0.0, 0.999, 40):
+        got.add(ops.sample(z.cuda(), 0.7, 5, 0.3, torch.tensor([r], dtype=torch.float32).cuda()).item())
+    assert got == {0, 1, 2}
 
 
 def test_sample_top_p_ties_keep_lower_indices():
