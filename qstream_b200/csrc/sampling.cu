@@ -142,9 +142,14 @@ sample_kernel(int32_t* __restrict__ out, const float* __restrict__ logits, int V
     // reaches what is still wanted.  (One bit per pass, 32 passes with a sum over the block each, took 150 us
     // of a 300 us kernel at a vocabulary of 50,400.)
     uint32_t k_key = 0;                              // keep everything
-    if (top_k > 0 && top_k < V) {
-        if (tid == 0) { sel_prefix = 0; sel_remaining = top_k; }
-        for (int shift = 24; shift >= 0; shift -= 8) {
+    // Without top-k, top-p alone mostly keeps a few elements too: the SAMPLE_LIST largest are listed as if k were
+    // that, with the sum over the whole row as the total; if their share does not reach p, the general way is gone.
+    const bool real_k = top_k > 0 && top_k < V;
+    const bool stand_in = !real_k && top_p > 0.f && top_p < 1.f;
+    const int k_sel = real_k ? top_k : min(V, SAMPLE_LIST);
+    if (real_k || stand_in) {
+        if (tid == 0) { sel_prefix = 0; sel_remaining = k_sel; }
+        for (int shift = 24; shift >= 0 && k_sel < V; shift -= 8) {
             if (tid < 256) hist[tid] = 0;
             __syncthreads();
             const uint32_t prefix = sel_prefix;
@@ -164,7 +169,7 @@ sample_kernel(int32_t* __restrict__ out, const float* __restrict__ logits, int V
             }
             __syncthreads();
         }
-        k_key = sel_prefix;
+        k_key = k_sel < V ? sel_prefix : 0u;
 
         // The elements that top-k keeps (k of them, and the ties at the k-th value) are few: they are listed,
         // put in the order that top-p wants (falling value, equal values by rising index), and one thread does
@@ -198,47 +203,59 @@ sample_kernel(int32_t* __restrict__ out, const float* __restrict__ logits, int V
             __syncthreads();
             const float top = s_y[0];
             for (int a = tid; a < m; a += blockDim.x) s_w[a] = expf(s_y[a] - top);
+            float z_row = 0.f;
+            if (stand_in) {                                          // the total is the whole row's
+                for (int i = tid; i < V; i += blockDim.x) z_row += expf(x[i] * inv_t - top);
+                z_row = block_sum(z_row, scratch);
+            }
             __syncthreads();
             if (tid == 0) {
                 int kept = m;
-                float z = 0.f;
-                for (int a = 0; a < m; ++a) z += s_w[a];
+                float z = z_row;
+                if (!stand_in)
+                    for (int a = 0; a < m; ++a) z += s_w[a];
                 if (top_p > 0.f && top_p < 1.f && z > 0.f) {
                     const float limit = top_p * z;
                     float run = 0.f;
-                    for (int a = 0; a < m; ++a) {
+                    bool found = false;
+                    for (int a = 0; a < m && !found; ++a) {
                         run += s_w[a];
-                        if (run > limit) { kept = a + 1; break; }
+                        if (run > limit) { kept = a + 1; found = true; }
                     }
-                }
+                    if (stand_in && !found && m < V) kept = -1;      // the list does not hold the whole of top-p
+                } else if (stand_in && m < V) kept = -1;
                 list_kept = kept;
             }
             __syncthreads();
             const int kept = list_kept;
-            for (int a = tid; a < kept; a += blockDim.x) {           // the kept ones by rising index
-                const int ia = s_i[a];
-                int rank = 0;
-                for (int b = 0; b < kept; ++b) rank += s_i[b] < ia ? 1 : 0;
-                l_i[rank] = ia;
-                l_y[rank] = s_w[a];
-            }
-            __syncthreads();
-            if (tid == 0) {
-                float total = 0.f;
-                for (int a = 0; a < kept; ++a) total += l_y[a];
-                const float target = draws[blockIdx.x] * total;
-                int r = -1, last = 0;
-                float run = 0.f;
-                for (int a = 0; a < kept; ++a) {
-                    if (!(l_y[a] > 0.f)) continue;                   // a weight of zero (or NaN) is never drawn
-                    last = l_i[a];
-                    run += l_y[a];
-                    if (r < 0 && run >= target) r = l_i[a];
+            if (kept >= 0) {
+                for (int a = tid; a < kept; a += blockDim.x) {           // the kept ones by rising index
+                    const int ia = s_i[a];
+                    int rank = 0;
+                    for (int b = 0; b < kept; ++b) rank += s_i[b] < ia ? 1 : 0;
+                    l_i[rank] = ia;
+                    l_y[rank] = s_w[a];
                 }
-                out[blockIdx.x] = r >= 0 ? r : last;                 // none reached the target: the last kept, else 0
+                __syncthreads();
+                if (tid == 0) {
+                    float total = 0.f;
+                    for (int a = 0; a < kept; ++a) total += l_y[a];
+                    const float target = draws[blockIdx.x] * total;
+                    int r = -1, last = 0;
+                    float run = 0.f;
+                    for (int a = 0; a < kept; ++a) {
+                        if (!(l_y[a] > 0.f)) continue;                   // a weight of zero (or NaN) is never drawn
+                        last = l_i[a];
+                        run += l_y[a];
+                        if (r < 0 && run >= target) r = l_i[a];
+                    }
+                    out[blockIdx.x] = r >= 0 ? r : last;                 // none reached the target: the last kept, else 0
+                }
+                return;
             }
-            return;
         }
+        if (stand_in) k_key = 0;                                     // the general way filters by top-p alone
+        __syncthreads();
     }
 
     float mx = -INFINITY;

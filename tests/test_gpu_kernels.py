@@ -257,7 +257,7 @@ def test_repeat_penalty():
 @pytest.mark.parametrize("V", [320, 50400])
 @pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 0, 1.0), (0.7, 40, 0.9), (1.3, 5, 1.0),
                                                      (0.9, 0, 0.5), (0.5, 1, 1.0), (1.0, 1000, 0.97), (0.9, 3000, 0.95),
-                                                     (1.1, 300, 1.0)])
+                                                     (1.1, 300, 1.0), (3.0, 0, 0.9), (0.6, 0, 0.95)])
 def test_sample_against_plain(V, temperature, top_k, top_p):
     """The chosen token's CDF interval in the plain pipeline must contain the draw (a
     little widened: 32-bit sums in another order)."""
