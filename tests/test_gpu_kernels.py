@@ -327,7 +327,9 @@ def test_sample_top_p_ties_keep_lower_indices():
 
 
 @pytest.mark.parametrize("H,Hkv,dh,window", [(4, 4, 16, 0), (16, 16, 256, 0), (6, 2, 48, 0), (2, 1, 80, 0),
-                                             (4, 4, 64, 300), (3, 3, 128, 0), (2, 2, 320, 0), (2, 2, 32, 1)])
+                                             (4, 4, 64, 300), (3, 3, 128, 0), (2, 2, 320, 0), (2, 2, 32, 1),
+                                             # head sizes whose chunks do not fill a power of two of lanes, and a window
+                                             (4, 2, 96, 0), (2, 2, 160, 0), (3, 1, 112, 0), (32, 32, 80, 100), (2, 2, 48, 1)])
 def test_decode_attention_kernel(H, Hkv, dh, window):
     """The split decode kernel (bfloat16) against the plain attention at many lengths: page and
     split edges, one key, a window."""
