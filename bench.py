@@ -23,7 +23,8 @@ architecture (16 prompts of unequal lengths with 256 decoded tokens each; a 2,04
 prefill and decode at batch 32 from 512-token prompts).  `--config` runs one shape alone;
 `--per-kernel` times each kernel of one layer by itself (CUDA events around a captured graph
 of many repeats, each repeat on another layer's weights so that nothing is served from L2) and prints a table of
-achieved GB/s or TFLOP/s against the measured peaks.
+achieved GB/s or TFLOP/s against the measured peaks.  `--batch B --context C --skip-points` times decode steps
+at another point; a context beyond the shape's 2,048 positions lengthens the position table and nothing else.
 
 Inputs are synthetic token ids, uniform over the vocabulary; each step reads more than
 5 GB, far more than the 126 MB L2, so no L2 flush is needed between steps.
@@ -135,14 +136,17 @@ def reference_arm():
 class Bench:
     """One model shape on the device, with the measurements that the JSON line is made of."""
 
-    def __init__(self, shape: str, n_layer: int, sampler: ClockSampler, pk: dict, seed: int = 0):
+    def __init__(self, shape: str, n_layer: int, sampler: ClockSampler, pk: dict, seed: int = 0, n_positions: int = 0):
         import numpy as np
         import torch
         import qstream_b200 as qs
         self.np, self.torch, self.qs = np, torch, qs
         self.shape, self.pk, self.sampler = shape, pk, sampler
         self.n_layer_full = SHAPES[shape]["n_layer"]
-        self.cfg = qs.GptjConfig.from_dict({**SHAPES[shape], "n_layer": n_layer or self.n_layer_full})
+        sizes = {**SHAPES[shape], "n_layer": n_layer or self.n_layer_full}
+        if n_positions > sizes["n_positions"]:            # a context beyond the shape's own: the same layers, a longer position table
+            sizes["n_positions"] = n_positions
+        self.cfg = qs.GptjConfig.from_dict(sizes)
         self.model = qs.CausalLM.random(self.cfg, seed=seed, dtype="bfloat16", device="cuda:0")
         self.rng = np.random.default_rng(seed)
         c = self.cfg
@@ -549,7 +553,7 @@ def main(argv=None) -> int:
                           "data": "synthetic token ids, random weights", args.config: out}))
         return 0
 
-    bench = Bench("gptj6b", args.layers, sampler, pk)
+    bench = Bench("gptj6b", args.layers, sampler, pk, n_positions=args.context)
     cfg, ctx = bench.cfg, args.context
     main_run = bench.decode_at_context(args.batch, ctx, args.steps, args.warmup)
     gbs = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
