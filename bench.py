@@ -423,7 +423,9 @@ def per_kernel(shape, layers, pk, batch, ctx, prefill_tokens=2048, repeats=56):
     from qstream_b200.parts.linear import linear
 
     n_layer = max(layers or 8, 4)
-    cfg = qs.GptjConfig.from_dict({**SHAPES[shape], "n_layer": n_layer})
+    sizes = {**SHAPES[shape], "n_layer": n_layer}
+    sizes["n_positions"] = max(sizes["n_positions"], ctx, prefill_tokens + 1)      # longer contexts: a longer position table
+    cfg = qs.GptjConfig.from_dict(sizes)
     model = qs.CausalLM.random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
     D, F, H, dh, V = cfg.n_embd, cfg.inner, cfg.n_head, cfg.head_dim, cfg.vocab_size
     rng = torch.Generator(device="cuda").manual_seed(0)

@@ -242,6 +242,18 @@ __device__ __forceinline__ bool wait_or_abort_grid(uint64_t* bar, uint32_t parit
     return false;
 }
 
+// Where tile number `tile` lies: tiles are walked group by group of `gm` pairs of row tiles, inside a group
+// column tile by column tile, rows fastest.  The rows of A that the CTA pairs work on at a time then stay
+// within one group, which the host sizes to fit L2: without groups, with more rows of A than L2 holds (8,192
+// tokens and more at K = 4096), every round of tiles read all of A from memory again.
+__device__ __forceinline__ void pair_tile_coords(int tile, int m_pairs, int n_tiles, int gm, int& m, int& n) {
+    const int per_group = gm * n_tiles;
+    const int g = tile / per_group, idx = tile - g * per_group;
+    const int here = min(gm, m_pairs - g * gm);       // the last group may hold fewer rows
+    n = idx / here;
+    m = g * gm + (idx - n * here);
+}
+
 // Two CTAs on neighbouring SMs work on one 256 x PAIR_BN output tile (PAIR_BN = 256, or 192 where that wastes
 // less of the last round of tiles) with tcgen05.mma.cta_group::2: each CTA
 // loads its own 128 rows of A and its own half of the W tile - half the shared-memory traffic
@@ -252,7 +264,7 @@ __device__ __forceinline__ bool wait_or_abort_grid(uint64_t* bar, uint32_t parit
 template <int PAIR_BN>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const Epilogue ep, const int K, const int m_pairs, const int n_tiles, const int splits,
+                    const Epilogue ep, const int K, const int m_pairs, const int n_tiles, const int splits, const int gm,
                     float* __restrict__ ws, int32_t* __restrict__ counters, int32_t* __restrict__ status) {
     constexpr int PAIR_STAGE = pair_stage<PAIR_BN>();
     constexpr int PAIR_STAGES = pair_stages<PAIR_BN>();
@@ -308,8 +320,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             };
             for (int t = pair; t < total_tiles && !*aborted; t += n_pairs_grid) {
                 const int tile = t / splits, part = t - tile * splits;
-                const int m0 = (tile % m_pairs) * 2 * BM + (int)rank * BM;
-                const int n0 = (tile / m_pairs) * PAIR_BN + (int)rank * (PAIR_BN / 2);
+                int tm, tn;
+                pair_tile_coords(tile, m_pairs, n_tiles, gm, tm, tn);
+                const int m0 = tm * 2 * BM + (int)rank * BM;
+                const int n0 = tn * PAIR_BN + (int)rank * (PAIR_BN / 2);
                 const int kb_end = (int)((long long)(part + 1) * num_kb / splits);
                 for (int kb = (int)((long long)part * num_kb / splits); kb < kb_end; ++kb, ++it) {
                     const int s = it % PAIR_STAGES;
@@ -364,7 +378,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int t = pair; t < total_tiles; t += n_pairs_grid, ++i) {
             const int buf = i & 1;
             const int tile = t / splits, part = t - tile * splits;
-            const int m = (tile % m_pairs) * 2 * BM + (int)rank * BM + r, n0 = (tile / m_pairs) * PAIR_BN;
+            int tm, tn;
+            pair_tile_coords(tile, m_pairs, n_tiles, gm, tm, tn);
+            const int m = tm * 2 * BM + (int)rank * BM + r, n0 = tn * PAIR_BN;
             // The tile's bias goes to shared memory once, before the wait for the sums: read per group of
             // columns from global memory it cost every thread 32 round trips in a row (a warp is alone on
             // its scheduler here, and loads do not move across the stores between them): 9 of the 21 us that
@@ -968,7 +984,15 @@ int launch_pair(const CUtensorMap& ma, const void* W, long long ldw, const Epilo
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 2;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<PAIR_BN>, ma, mw, ep, K, m_pairs, n_tiles, (int)splits,
+    // Rows of A per group of tiles: 32 MB, about a quarter of L2 (126 MB here), at least one pair of row tiles.
+    // Measured with groups of 16, 32 and 64 MB against none: 16,384 tokens 2005 -> 1559 us (x 16384 x 4096), 1661 ->
+    // 1234 us (x 12288 x 4096), 2327 -> 2014 us (x 4096 x 20480) at 32 MB; 8,192 tokens 5 to 7 % faster; 4,096
+    // tokens the same; at 2,048 tokens the product over K = 20480 was 2 % slower in groups, so up to there
+    // the tiles keep the plain order.
+    long long gm = ((long long)32 << 20) / ((long long)2 * BM * K * 2);
+    if (gm < 1) gm = 1;
+    if (gm > m_pairs || m_pairs <= 8) gm = m_pairs;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<PAIR_BN>, ma, mw, ep, K, m_pairs, n_tiles, (int)splits, (int)gm,
                                        ws, counters, status);
     if (e != cudaSuccess) return qs_fail(QS_ERR_INTERNAL, "gemm_tc pair: %s", cudaGetErrorString(e));
     return qs_check_launch("gemm_tc pair");

@@ -22,6 +22,8 @@ SHAPES = [(1, 128, 64), (1, 4096, 4096), (3, 200, 96), (8, 320, 320), (16, 64, 2
           (129, 136, 64), (257, 520, 136), (383, 1000, 192), (640, 1288, 72),
           # CTA pairs: more tiles than pairs, with and without a whole round of them
           (1000, 1288, 4096), (2048, 4096, 1024), (300, 9000, 1536),
+          # more than 2,048 tokens: tiles walked in groups of rows (here groups of 1, 3 and 16 pairs of row tiles)
+          (2304, 520, 40960), (2560, 1000, 20480), (4352, 264, 4096),
           # few tokens: tiles of 88, 112 and 120 rows, a last tile that reaches past N, more tiles than SMs
           (8, 12288, 256), (64, 16384, 128), (4, 50400, 128), (40, 2104, 320), (2, 19000, 64),
           # 65 to 128 tokens still stream the weights (128 tokens on the N side), with and without cuts along K
