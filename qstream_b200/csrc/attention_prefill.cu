@@ -89,7 +89,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t* p_full = s_full + 2;                        // [2]
     uint64_t* p_free = p_full + 2;                        // [2]
     uint64_t* pv_done = p_free + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
+    uint64_t* o_done = pv_done + 1;                       // the last P V of the tile has completed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
     volatile uint32_t* aborted = tmem_slot + 1;
     uint16_t* row_max = reinterpret_cast<uint16_t*>(bars + 64);    // [2 buffers][2 halves][BM], 512 bytes behind the barriers
 
@@ -115,6 +116,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         mbar_init(&p_free[0], 1);
         mbar_init(&p_free[1], 1);
         mbar_init(pv_done, 1);
+        mbar_init(o_done, 1);
         *aborted = 0;
         mbar_fence_init();
         prefetch_tensormap(&map_q);
@@ -213,6 +215,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 mma_commit(&p_free[j & 1]);
                 mma_commit(pv_done);
             }
+            // The end of the tile has a barrier of its own.  `pv_done` only tells its phases apart by their
+            // parity, and a softmax thread that has not waited for it in the last blocks (no rescaling) may reach
+            // the end while the last but one P V is still running: a wait for the last one's parity then
+            // passes at once, and the thread would read O - and reuse the weights' buffers - too early.
+            mma_commit(o_done);
             if (!ok || *aborted) {                   // let the softmax warps fall through their waits
                 mma_commit(&s_full[0]); mma_commit(&s_full[1]); mma_commit(pv_done);
                 mma_commit(&p_free[0]); mma_commit(&p_free[1]);
@@ -319,7 +326,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 mbar_arrive(&p_full[j & 1]);
             }
         }
-        if (ok && !mbar_wait(pv_done, (n_blocks - 1) & 1)) { atomicExch(status, 118); ok = false; }
+        if (ok && !mbar_wait(o_done, 0)) { atomicExch(status, 118); ok = false; }
         // the row's sum: the two partial sums in the order of their columns
         float* lsum = reinterpret_cast<float*>(p_smem);   // the weights' buffers are free now
         asm volatile("bar.sync 1, 256;" ::: "memory");    // every thread has seen the last P V complete (or given up)

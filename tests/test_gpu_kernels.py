@@ -451,6 +451,33 @@ def test_prefill_attention_kernel(H, Hkv, dh, window):
         np.testing.assert_allclose(f64(torch.cat(outs[i])), ref, atol=3e-2, rtol=3e-2, err_msg=f"sequence {i} of {n}")
 
 
+def test_prefill_attention_gives_the_same_bits_every_time():
+    """Sixteen prompts of unequal lengths in one step, a thousand times over the same inputs, with what earlier
+    sequences left in the pages still there: every launch must give the same bits.  (A softmax thread that
+    had not rescaled in a tile's last blocks could pass the wait for the last P V while the one before it
+    was still running, read O early and overwrite weights that the tensor core was still reading: two
+    launches in three hundred gave other values, NaN among them, in the rows of one tile.)"""
+    from qstream_b200.csrc import attention_bf16
+    lens = [77, 427, 31, 472, 237, 413, 591, 579, 185, 586, 522, 116, 190, 250, 448, 217]
+    H, dh = 16, 256
+    case = PagedCase("bfloat16", lens, H, H, dh, seed=1, n_slots=16, fill=0.0)
+    case.v_cache.normal_(0, 3.0)
+    case.k_cache.normal_(0, 1.0)
+    tdev = case.table.cuda()
+    ranges = [(i, 0, n) for i, n in enumerate(lens)]
+    q, k, v, slot, pos = case.packed(ranges)
+    ops.rope_store(None, k, v, 0, H, dh, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+    tiles = _tiles(ranges, case.slots)
+    first = attention_bf16.prefill(q, H, H, dh, dh ** -0.5, 0, tiles, tdev, case.pt, case.k_cache, case.v_cache, case.status).clone()
+    different = 0
+    for _ in range(1000):                           # each launch starts on an idle device: that is when it showed
+        o = attention_bf16.prefill(q, H, H, dh, dh ** -0.5, 0, tiles, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+        different += 0 if torch.equal(o, first) else 1
+    assert different == 0
+    assert int(case.status.item()) == 0
+    assert torch.isfinite(first.float()).all()
+
+
 def test_prefill_attention_finds_one_far_key_and_keeps_rows_apart():
     from qstream_b200.csrc import attention_bf16
     H, dh, n = 2, 64, 600
