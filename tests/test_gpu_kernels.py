@@ -501,3 +501,42 @@ def test_prefill_attention_finds_one_far_key_and_keeps_rows_apart():
         t = 300
         lo = 0 if window == 0 else t - window + 1
         np.testing.assert_allclose(f64(o[t]).reshape(H, dh), f64(case.v[0][lo:t + 1]).mean(0), atol=5e-2)
+
+
+def test_kernels_give_the_same_bits_every_time():
+    """Every kernel whose work is shared out between CTAs that meet again (partial tiles and arrival counters in the
+    products, splits and their merge in the decode attention, counts and lists in the sampler), launched two
+    hundred times on an idle device over the same inputs: the same bits each time."""
+    import math
+    from qstream_b200.csrc import attention_bf16, gemm_tc
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def same(fn, reps=200):
+        first = fn().clone()
+        return all(torch.equal(fn(), first) for _ in range(reps))
+
+    for M, N, K in [(8, 4096, 20480), (64, 4096, 20480), (1, 4096, 4096), (256, 4096, 20480), (300, 520, 16384), (2600, 1000, 4096)]:
+        x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).bfloat16()
+        b = torch.randn(N, device="cuda", generator=g).bfloat16()
+        r = torch.randn(M, N, device="cuda", generator=g).bfloat16()
+        assert same(lambda: gemm_tc.linear(x, w, b, "gelu_new", (r,))), (M, N, K)
+    gemm_tc.check_status(torch.device("cuda"))
+    lens = [2043, 1, 300, 1488, 64, 65, 700, 1025]
+    H, dh = 16, 256
+    case = PagedCase("bfloat16", lens, H, H, dh, seed=2, n_slots=10, fill=0.0)
+    case.v_cache.normal_(0, 3.0)
+    case.k_cache.normal_(0, 1.0)
+    tdev = case.table.cuda()
+    q, k, v, slot, pos = case.packed([(i, 0, n) for i, n in enumerate(lens)])
+    ops.rope_store(None, k, v, 0, H, dh, 0, None, slot, pos, tdev, case.pt, case.k_cache, case.v_cache, case.status)
+    ql = q[torch.as_tensor(np.cumsum(lens) - 1).cuda()].contiguous()
+    slot_l = torch.tensor(case.slots, dtype=torch.int32).cuda()
+    pos_l = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    assert same(lambda: attention_bf16.decode(ql, H, H, dh, dh ** -0.5, 0, slot_l, pos_l, tdev, case.pt, case.k_cache,
+                                              case.v_cache, 2048, case.status))
+    assert int(case.status.item()) == 0
+    logits = torch.randn(16, 50400, device="cuda", generator=g)
+    draws = torch.rand(16, device="cuda", generator=g)
+    assert same(lambda: ops.sample(logits, 0.7, 40, 0.9, draws))
+    assert same(lambda: ops.sample(logits, 0.7, 0, 0.9, draws))
