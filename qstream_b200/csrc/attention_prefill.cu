@@ -271,7 +271,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const float mine = round_up_16(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])));
             uint16_t* xch = row_max + (j & 1) * 2 * BM;   // two buffers: block j + 2 writes only after everyone passed barrier j + 1
             xch[half * BM + r] = (uint16_t)(__float_as_uint(mine) >> 16);
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");      // the row's two threads sit in warps quad + 2 and quad + 6: a barrier of their own per quarter
             const float theirs = __uint_as_float((uint32_t)xch[(half ^ 1) * BM + r] << 16);
             const float bmax = fmaxf(mine, theirs) * scale_log2;                      // scale_log2 > 0
             // Two buffers of weights: this block's buffer is free once the P V of block j - 2 has completed
@@ -329,9 +329,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (ok && !mbar_wait(o_done, 0)) { atomicExch(status, 118); ok = false; }
         // the row's sum: the two partial sums in the order of their columns
         float* lsum = reinterpret_cast<float*>(p_smem);   // the weights' buffers are free now
-        asm volatile("bar.sync 1, 256;" ::: "memory");    // every thread has seen the last P V complete (or given up)
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
         lsum[half * BM + r] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
         const float l_all = lsum[r] + lsum[BM + r];
         if (ok && !*aborted) {
             tc_fence_after_sync();
