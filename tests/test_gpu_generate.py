@@ -177,3 +177,30 @@ def test_interrupt_from_a_callback(tmp_path):
     # the engine serves the next call as if nothing had happened
     res = gen.generate([[1, 2, 3]], max_new_tokens=4, sampling=qs.SamplingConfig.greedy(), stop_tokens=())
     assert res.finish_reasons == ["length"] and len(res.tokens[0]) == 4
+
+
+@pytest.mark.parametrize("which,dtype", [("A", "bfloat16"), ("B", "bfloat16"), ("B", "float32")])
+def test_the_same_requests_give_the_same_tokens_again(tmp_path, which, dtype):
+    """Sixty batches of random requests (unequal prompts, stop tokens, greedy and sampled, slots and pages
+    used again and again) through two engines on the same model: the same tokens and the same reasons
+    for stopping, request by request.  Nothing in a step may depend on timing."""
+    folder, cfg = make_folder(tmp_path, which, dtype)
+    model = qs.load_model(folder, dtype=dtype, device="cuda")
+    runs = []
+    for rep in range(2):
+        eng = qs.Engine(model, max_tokens=64 * 60, max_batch=8)
+        rng = np.random.default_rng(11)
+        outs = []
+        for _ in range(60):
+            n = int(rng.integers(1, 9))
+            prompts = [random_tokens(rng, int(rng.integers(1, cfg.n_positions - 45)), cfg.vocab_size) for _ in range(n)]
+            stop = (int(rng.integers(0, cfg.vocab_size)),) if rng.random() < 0.5 else ()
+            sampling = qs.SamplingConfig.greedy() if rng.random() < 0.6 else qs.SamplingConfig(
+                temperature=0.8, top_k=20, top_p=0.9, repeat_penalty=1.1, seed=int(rng.integers(0, 1000)))
+            res = qs.generate(eng, prompts, max_new_tokens=int(rng.integers(1, 40)), sampling=sampling, stop_tokens=stop)
+            outs.append((res.tokens, res.finish_reasons))
+        eng.cache.check()
+        eng.check_status()
+        runs.append(outs)
+    for i, (a, b) in enumerate(zip(*runs)):
+        assert a == b, f"batch {i}"
