@@ -879,7 +879,7 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
 
 template <int BN>
 int launch_stream(const void* W, long long ldw, const CUtensorMap& ma, const Epilogue& ep, int N, int K, float* ws,
-                  long long ws_floats, int32_t* counters, int n_counters, int32_t* status, cudaStream_t stream) {
+                  long long ws_floats, int32_t* counters, int n_counters, int32_t* status, int smem_kb, cudaStream_t stream) {
     static bool configured = false;
     static int sm_count = 0;
     constexpr int SMEM_MAX = 224 * 1024;
@@ -914,7 +914,10 @@ int launch_stream(const void* W, long long ldw, const CUtensorMap& ma, const Epi
     long long G = tiles * splits;
     if (splits > 1 && (tiles > n_counters || G * 2 * BN * BM > ws_floats)) G = tiles;
     const int stage = (int)rows * BK * 2 + BN * BK * 2;
-    int stages = (SMEM_MAX - 2048 - STREAM_PAD) / stage;
+    // the caller may bound a CTA's shared memory, so that CTAs of two products (on two streams) share an SM
+    const int smem_limit = smem_kb > 0 && smem_kb * 1024 < SMEM_MAX ? smem_kb * 1024 : SMEM_MAX;
+    int stages = (smem_limit - 2048 - STREAM_PAD) / stage;
+    if (stages < 2) stages = 2;
     if (stages > MAX_STREAM_STAGES) stages = MAX_STREAM_STAGES;
     const int smem = 2048 + stages * stage + STREAM_PAD;
     CUtensorMap mw;
@@ -1029,10 +1032,12 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mw, const Epilog
 // ws / counters: scratch for split-K in the weight-streaming arrangement (M <= 128): `ws_floats` floats
 // and `n_counters` int32 that are ZERO before the first call (the kernel leaves them zero).  Without
 // them (null) the product runs unsplit.  Calls that share the scratch must not overlap on the GPU.
+// `smem_kb` > 0 bounds the shared memory of a CTA of the weight-streaming arrangement (M <= 128): with half of
+// an SM's each, the CTAs of two products that run on two streams share the SMs instead of taking turns.
 QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const void* bias, int bias_dtype, int act,
                       const void* res1, const void* res2, int M, int N, int K, long long lda, long long ldw,
                       long long ldc, long long ldr, float* ws, long long ws_floats, int32_t* counters, int n_counters,
-                      int32_t* status, cudaStream_t stream) {
+                      int32_t* status, int smem_kb, cudaStream_t stream) {
     if (M == 0 || N == 0) return QS_OK;
     QS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     QS_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ldw >= K,
@@ -1072,8 +1077,8 @@ QS_API int qs_gemm_tc(void* C, int c_dtype, const void* A, const void* W, const 
     }
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     if ((rc = tensor_map(&ma, A, M, K, lda, bn)) != QS_OK) return rc;
-    if (bn == 16) return launch_stream<16>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    if (bn == 32) return launch_stream<32>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    if (bn == 64) return launch_stream<64>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
-    return launch_stream<128>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, stream);
+    if (bn == 16) return launch_stream<16>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, smem_kb, stream);
+    if (bn == 32) return launch_stream<32>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, smem_kb, stream);
+    if (bn == 64) return launch_stream<64>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, smem_kb, stream);
+    return launch_stream<128>(W, ldw, ma, ep, N, K, ws, ws_floats, counters, n_counters, status, smem_kb, stream);
 }

@@ -17,7 +17,7 @@ def _entry():
     if _fn is None:
         _fn = ops.bind("qs_gemm_tc", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                                      c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
+                                      c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p])
     return _fn
 
 
@@ -48,6 +48,23 @@ class second_scratch:
     def __exit__(self, *exc):
         global scratch_slot
         scratch_slot = self.before
+
+
+smem_limit_kb = 0               # what a CTA of the weight-streaming product may take of its SM's shared memory (0 = all)
+
+
+class shared_sms:
+    """Products of few tokens launched inside this context take half of an SM's shared memory each, so that the
+    CTAs of two of them - one on each of two streams - sit on the same SMs and stream their weights together
+    instead of taking turns."""
+
+    def __enter__(self):
+        global smem_limit_kb
+        self.before, smem_limit_kb = smem_limit_kb, 111
+
+    def __exit__(self, *exc):
+        global smem_limit_kb
+        smem_limit_kb = self.before
 
 
 def scratch(device):
@@ -100,5 +117,5 @@ def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, 
                        ops.dtype_code(bias) if bias is not None else 0, ops.ACTIVATIONS[activation],
                        ops.ptr(res[0]), ops.ptr(res[1]), M, N, K, x.stride(0), weight.stride(0), out.stride(0), ldr,
                        ops.ptr(ws), ws.numel(), ops.ptr(counters), counters.numel(),
-                       ops.ptr(status_word(x.device)), ops.stream()))
+                       ops.ptr(status_word(x.device)), int(smem_limit_kb), ops.stream()))
     return out

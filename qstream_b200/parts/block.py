@@ -8,6 +8,8 @@ the layer.
 """
 from __future__ import annotations
 
+import contextlib
+
 from ..errors import QsError, QStreamError
 from .base import Part, part_class, register
 
@@ -115,15 +117,17 @@ class ParallelBlock(Arrangement):
         side = getattr(step, "side_stream", None)
         if (side is not None and b.decode and self.key_bytes is not None
                 and h.shape[0] * (b.max_total or step.cache.max_context) * self.key_bytes <= SIDE_BRANCH_SHARE * self.ffn_bytes):
-            from .linear import beside_main_stream
+            from .linear import beside_main_stream, shared_sms
             # m is read on the main stream, so it comes from the main stream's memory; g lives on the second stream only
             m = torch.empty((h.shape[0], self.fused_weight.shape[0]), dtype=h.dtype, device=h.device)
-            with beside_main_stream(side, h.device) as beside:
-                g = self.ffn.forward_hidden(h, step)
-                linear(g, self.fused_weight[:, self.k_mixer:], self.fused_bias, out=m)
-            o = self.mixer.forward_hidden(h, step, cache_id)
-            beside.join()
-            return linear(o, self.fused_weight[:, :self.k_mixer], None, residuals=(x, m))
+            # the two streams' products side by side on every SM (up to 8 rows: +1 to +5 % tokens a second; 16 rows: -1 %)
+            with shared_sms() if h.shape[0] <= 8 else contextlib.nullcontext():
+                with beside_main_stream(side, h.device) as beside:
+                    g = self.ffn.forward_hidden(h, step)
+                    linear(g, self.fused_weight[:, self.k_mixer:], self.fused_bias, out=m)
+                o = self.mixer.forward_hidden(h, step, cache_id)
+                beside.join()
+                return linear(o, self.fused_weight[:, :self.k_mixer], None, residuals=(x, m))
         hidden = torch.empty((h.shape[0], self.fused_weight.shape[1]), dtype=h.dtype, device=h.device)
         self.mixer.forward_hidden(h, step, cache_id, out=hidden[:, :self.k_mixer])
         self.ffn.forward_hidden(h, step, out=hidden[:, self.k_mixer:])

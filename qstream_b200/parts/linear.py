@@ -22,6 +22,12 @@ def linear(x, weight, bias=None, activation=None, residuals=(), out_dtype=None, 
     return ops.linear_simt(x, weight, bias, activation, residuals, out_dtype, out)
 
 
+def shared_sms():
+    """A context in which the tensor-core products of few tokens leave half of each SM to another product."""
+    from ..csrc import gemm_tc
+    return gemm_tc.shared_sms()
+
+
 class beside_main_stream:
     """Enter a second CUDA stream that has waited for everything the current stream holds so far; products
     inside use a scratch of their own.  `join()` afterwards makes the current stream wait for the second."""
