@@ -67,10 +67,14 @@ class Arrangement(Part):
 # A decode step runs a parallel block's two branches side by side while the keys and values its rows read
 # (rows x the longest sequence x the mixer's bytes per key) stay below this share of the feed-forward's
 # weights: then the attention kernels are bound by latency, beyond it by memory like the products.
-# Measured on a B200 against the one fused product, tokens a second: GPT-J-6B's sizes +7 to +13 % up to a share
-# of 0.25 (1 x 2,048 keys, 4 x 1,024, 8 x 512, 16 x 256), -3 to -5 % from 0.5 on; CodeGen-16B's +10 to +13 %
-# up to 0.17, +3 to +4 % at 0.33, +1 % at 0.67; CodeGen-2B's +12 to +14 % up to 0.2, +1 to +3 % at 0.4, -1.5 % at 0.8.
-SIDE_BRANCH_SHARE = 0.35
+# Up to 8 rows the two streams' products also share the SMs (see `forward`), which moves the limit up.
+# Measured on a B200 against the one fused product, tokens a second, GPT-J-6B's sizes: up to 8 rows +1 to +8 %
+# up to a share of 0.5 (1 x 2,048 keys ... 8 x 1,024), -10 % at 0.6 (8 x 1,280); 16 rows and more +6 to +7 % up
+# to 0.25 (16 x 256), -5 % at 0.5 (16 x 512).  CodeGen-16B's sizes: +5 to +13 % up to 0.33, +1.5 % at 0.67.
+# CodeGen-2B's: +11 to +14 % up to 0.4, -1 to -2 % at 0.8.
+SIDE_BRANCH_SHARE = 0.5                 # up to SHARED_SM_ROWS rows
+SIDE_BRANCH_SHARE_MANY_ROWS = 0.35      # beyond
+SHARED_SM_ROWS = 8
 
 
 class ParallelBlock(Arrangement):
@@ -115,13 +119,14 @@ class ParallelBlock(Arrangement):
         from .linear import linear
         b = step.batch
         side = getattr(step, "side_stream", None)
+        share = SIDE_BRANCH_SHARE if h.shape[0] <= SHARED_SM_ROWS else SIDE_BRANCH_SHARE_MANY_ROWS
         if (side is not None and b.decode and self.key_bytes is not None
-                and h.shape[0] * (b.max_total or step.cache.max_context) * self.key_bytes <= SIDE_BRANCH_SHARE * self.ffn_bytes):
+                and h.shape[0] * (b.max_total or step.cache.max_context) * self.key_bytes <= share * self.ffn_bytes):
             from .linear import beside_main_stream, shared_sms
             # m is read on the main stream, so it comes from the main stream's memory; g lives on the second stream only
             m = torch.empty((h.shape[0], self.fused_weight.shape[0]), dtype=h.dtype, device=h.device)
             # the two streams' products side by side on every SM (up to 8 rows: +1 to +5 % tokens a second; 16 rows: -1 %)
-            with shared_sms() if h.shape[0] <= 8 else contextlib.nullcontext():
+            with shared_sms() if h.shape[0] <= SHARED_SM_ROWS else contextlib.nullcontext():
                 with beside_main_stream(side, h.device) as beside:
                     g = self.ffn.forward_hidden(h, step)
                     linear(g, self.fused_weight[:, self.k_mixer:], self.fused_bias, out=m)

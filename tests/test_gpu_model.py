@@ -442,6 +442,7 @@ def test_both_arrangements_of_the_parallel_block(tmp_path, which, monkeypatch):
     outs = {}
     for keys, graphs in ((0, True), (1 << 30, True), (1 << 30, False)):
         monkeypatch.setattr(block, "SIDE_BRANCH_SHARE", float(keys))
+        monkeypatch.setattr(block, "SIDE_BRANCH_SHARE_MANY_ROWS", float(keys))
         eng = qs.Engine(qs.load_model(folder, dtype="bfloat16", device="cuda"), max_tokens=1024, max_batch=8, use_graphs=graphs)
         assert all(b.fused_weight is not None for b in eng.model.blocks)
         slots = [eng.acquire() for _ in prompts]
